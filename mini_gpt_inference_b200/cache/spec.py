@@ -24,10 +24,16 @@ class PagedKVSpec:
     # needs more), if that is fewer.
     page_tokens: int | None = None
     num_pages: int | None = None
+    # Size of a value head where it differs from a key head's (None: ``head_dim``).
+    v_head_dim: int | None = None
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
     def __post_init__(self) -> None:
-        if self.n_kv_head <= 0 or self.head_dim <= 0:
-            raise ValueError("n_kv_head and head_dim must be positive")
+        if self.n_kv_head <= 0 or self.head_dim <= 0 or self.value_dim <= 0:
+            raise ValueError("n_kv_head, head_dim and v_head_dim must be positive")
         if self.window is not None and self.window <= 0:
             raise ValueError("window must be positive when given")
         if self.page_tokens is not None and self.page_tokens <= 0:

@@ -1,7 +1,7 @@
 """Device storage behind the cache manager's page ids and state slots.
 
 One tensor pair per layer group, laid out ``[layer in group, page, kv head, token in
-page, head_dim]``: the ``page_tokens x head_dim`` tile of one head is contiguous, so an
+page, head_dim]`` (values with their own size where a group's keys and values differ): the ``page_tokens x head_dim`` tile of one head is contiguous, so an
 attention kernel streams whole tiles.  (The reference keeps ``(num_blocks, block_size,
 H, D)`` per layer, src/minigpt_infer/cache/paged.py:109-123.)  State layers get one
 tensor ``[slot, *shape]`` each.  Storage is sized once, from the pool sizes.
@@ -21,7 +21,7 @@ class PagedKVView:
     """What an attention layer sees of the cache in one step."""
 
     k_pages: torch.Tensor          # [page, kv head, page_tokens, head_dim]
-    v_pages: torch.Tensor
+    v_pages: torch.Tensor          # [page, kv head, page_tokens, value size]
     group: int
     page_tokens: int
     window: int | None
@@ -45,7 +45,7 @@ class CacheStorage:
             shape = (len(group.layers), group.num_pages, group.spec.n_kv_head,
                      group.page_tokens, group.spec.head_dim)
             self.k.append(torch.zeros(shape, dtype=dtype, device=self.device))
-            self.v.append(torch.zeros(shape, dtype=dtype, device=self.device))
+            self.v.append(torch.zeros((*shape[:-1], group.spec.value_dim), dtype=dtype, device=self.device))
         self.state: dict[int, torch.Tensor] = {}
         for layer, spec in manager.state_layers.items():
             self.state[layer] = torch.zeros((manager.max_requests, *spec.shape),
@@ -65,6 +65,6 @@ class CacheStorage:
     def bytes_per_token(self) -> int:
         total = 0
         for g, group in enumerate(self.manager.groups):
-            total += (2 * len(group.layers) * group.spec.n_kv_head * group.spec.head_dim
-                      * self.k[g].element_size())
+            total += (len(group.layers) * group.spec.n_kv_head
+                      * (group.spec.head_dim + group.spec.value_dim) * self.k[g].element_size())
         return total

@@ -2,7 +2,7 @@
 
 The reference has a single model class and no registry (src/minigpt_infer/loader.py:88-136
 builds ``GPT`` directly).  Here ``config.json`` names the architecture
-(``architectures[0]`` or ``model_type``) and everything else — the loader, the
+(``architectures[0]``, ``architecture`` or ``model_type``) and everything else — the loader, the
 engine, the replay program — asks this registry for it.
 
 A family is a pair: a configuration class with ``from_dict`` and a function that
@@ -52,6 +52,8 @@ def architecture_name(raw: Mapping[str, Any]) -> str:
         return str(archs[0])
     if isinstance(archs, str):
         return archs
+    if isinstance(raw.get("architecture"), str) and raw["architecture"]:
+        return raw["architecture"]
     if raw.get("model_type"):
         return str(raw["model_type"])
     return DEFAULT_ARCHITECTURE
@@ -84,4 +86,4 @@ def load_config(model_dir) -> tuple[ModelFamily, Any]:
 
 def _ensure_builtin_models() -> None:
     # Importing the module registers the family; done lazily to avoid an import cycle.
-    from ..models import minigpt  # noqa: F401
+    from ..models import fakilorn, minigpt  # noqa: F401

@@ -23,10 +23,11 @@ constexpr int MAX_DPL = 8;   // head_dim <= 256: at most 8 dims per lane
 
 template <typename T>
 __global__ void __launch_bounds__(32 * WARPS)
-paged_attention_generic_kernel(const T* __restrict__ qkv, const T* __restrict__ k_pages,
+paged_attention_generic_kernel(const T* __restrict__ qkv, int q_stride, const T* __restrict__ k_pages,
                                const T* __restrict__ v_pages, const int* __restrict__ block_table,
                                const int* __restrict__ token_request, const int* __restrict__ positions,
-                               T* __restrict__ out, int n_tokens, int n_head, int n_kv_head, int head_dim,
+                               T* __restrict__ out, int n_tokens, int n_head, int n_kv_head, int head_dim, int v_dim,
+                               const T* __restrict__ gate, int gate_stride,
                                int page_tokens, int max_pages, int window, float scale, int num_pages,
                                int n_requests) {
     extern __shared__ float q_smem[];                     // [WARPS][head_dim]
@@ -35,11 +36,10 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, const T* __restrict__ 
     const int head = blockIdx.y * WARPS + warp;
     if (head >= n_head) return;                            // whole warp leaves together
     const int kv_head = head / (n_head / n_kv_head);
-    const int qkv_width = (n_head + 2 * n_kv_head) * head_dim;
     int p = positions[token];
     if (p < 0) {                                           // padding row of a fixed-size batch
-        T* pad = out + (size_t)token * n_head * head_dim + (size_t)head * head_dim;
-        for (int d = lane; d < head_dim; d += 32) pad[d] = from_float<T>(0.f);
+        T* pad = out + (size_t)token * n_head * v_dim + (size_t)head * v_dim;
+        for (int d = lane; d < v_dim; d += 32) pad[d] = from_float<T>(0.f);
         return;
     }
     // (guarded builds: a position beyond the block table, a request beyond its rows or a page beyond
@@ -51,7 +51,7 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, const T* __restrict__ 
     const int* table = block_table + (size_t)request * max_pages;
 
     float* q = q_smem + warp * head_dim;
-    const T* qrow = qkv + (size_t)token * qkv_width + (size_t)head * head_dim;
+    const T* qrow = qkv + (size_t)token * q_stride + (size_t)head * head_dim;
     for (int d = lane; d < head_dim; d += 32) q[d] = to_float(qrow[d]) * scale;
     __syncwarp();
 
@@ -85,32 +85,42 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, const T* __restrict__ 
         for (int jj = 0; jj < count; ++jj) {
             const float pj = __shfl_sync(0xffffffffu, prob, jj);
             const int rj = __shfl_sync(0xffffffffu, row, jj);
-            const T* vr = v_pages + (size_t)rj * head_dim;
+            const T* vr = v_pages + (size_t)rj * v_dim;
 #pragma unroll
             for (int i = 0; i < MAX_DPL; ++i) {
                 const int d = lane + 32 * i;
-                if (d < head_dim) acc[i] = fmaf(pj, to_float(vr[d]), acc[i]);
+                if (d < v_dim) acc[i] = fmaf(pj, to_float(vr[d]), acc[i]);
             }
         }
     }
     const float inv = 1.0f / run_sum;
-    T* orow = out + (size_t)token * n_head * head_dim + (size_t)head * head_dim;
+    T* orow = out + (size_t)token * n_head * v_dim + (size_t)head * v_dim;
+    // an output gate: each feature times the logistic function of its gate value (32-bit)
+    const T* grow = gate ? gate + (size_t)token * gate_stride + (size_t)head * v_dim : nullptr;
 #pragma unroll
     for (int i = 0; i < MAX_DPL; ++i) {
         const int d = lane + 32 * i;
-        if (d < head_dim) orow[d] = from_float<T>(acc[i] * inv);
+        if (d < v_dim) {
+            float o = acc[i] * inv;
+            if (grow) o *= 1.0f / (1.0f + expf(-to_float(grow[d])));
+            orow[d] = from_float<T>(o);
+        }
     }
 }
 
 }  // namespace
 
-// qkv: [n_tokens, (n_head + 2 n_kv_head) * head_dim]; pages: [page, kv head, page_tokens, head_dim];
-// block_table: [n_requests, max_pages]; out: [n_tokens, n_head * head_dim].  window <= 0: none.
+// q: rows of `q_stride` elements whose first n_head * head_dim hold the queries; key pages
+// [page, kv head, page_tokens, head_dim], value pages [page, kv head, page_tokens, v_dim] (keys and
+// values may differ in size); block_table: [n_requests, max_pages]; out: [n_tokens, n_head * v_dim].
+// gate (may be null): rows of `gate_stride` elements whose first n_head * v_dim hold gate values; the
+// output is multiplied by their logistic function.  window <= 0: none.
 // num_pages: pages of the pool (with n_requests, what guarded builds hold the indices against).
-MG_API int mg_paged_attention_generic(const void* qkv, const void* k_pages, const void* v_pages,
+MG_API int mg_paged_attention_general(const void* q, int q_stride, const void* k_pages, const void* v_pages,
                                       const int* block_table, const int* token_request,
                                       const int* positions, void* out, int n_tokens, int n_head,
-                                      int n_kv_head, int head_dim, int page_tokens, int max_pages,
+                                      int n_kv_head, int head_dim, int v_dim, const void* gate, int gate_stride,
+                                      int page_tokens, int max_pages,
                                       int window, float scale, int num_pages, int n_requests, int is_bf16,
                                       void* stream) {
     if (n_tokens == 0) return MG_OK;
@@ -118,18 +128,37 @@ MG_API int mg_paged_attention_generic(const void* qkv, const void* k_pages, cons
                "attention: bad sizes");
     MG_REQUIRE(n_head % n_kv_head == 0, "attention: n_head %d is not a multiple of n_kv_head %d", n_head, n_kv_head);
     MG_REQUIRE(head_dim > 0 && head_dim <= 32 * MAX_DPL, "attention: head_dim %d is outside 1..%d", head_dim, 32 * MAX_DPL);
+    MG_REQUIRE(v_dim > 0 && v_dim <= 32 * MAX_DPL, "attention: value size %d is outside 1..%d", v_dim, 32 * MAX_DPL);
+    MG_REQUIRE(q_stride >= n_head * head_dim && (gate == nullptr || gate_stride >= n_head * v_dim),
+               "attention: rows shorter than their heads");
     MG_REQUIRE(ceil_div(n_head, WARPS) <= 65535, "attention: too many heads");
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(n_tokens, ceil_div(n_head, WARPS)), block(32 * WARPS);
     const size_t smem = (size_t)WARPS * head_dim * sizeof(float);
     if (is_bf16)
         paged_attention_generic_kernel<bf16><<<grid, block, smem, s>>>(
-            (const bf16*)qkv, (const bf16*)k_pages, (const bf16*)v_pages, block_table, token_request, positions,
-            (bf16*)out, n_tokens, n_head, n_kv_head, head_dim, page_tokens, max_pages, window, scale, num_pages, n_requests);
+            (const bf16*)q, q_stride, (const bf16*)k_pages, (const bf16*)v_pages, block_table, token_request, positions,
+            (bf16*)out, n_tokens, n_head, n_kv_head, head_dim, v_dim, (const bf16*)gate, gate_stride, page_tokens,
+            max_pages, window, scale, num_pages, n_requests);
     else
         paged_attention_generic_kernel<float><<<grid, block, smem, s>>>(
-            (const float*)qkv, (const float*)k_pages, (const float*)v_pages, block_table, token_request, positions,
-            (float*)out, n_tokens, n_head, n_kv_head, head_dim, page_tokens, max_pages, window, scale, num_pages, n_requests);
+            (const float*)q, q_stride, (const float*)k_pages, (const float*)v_pages, block_table, token_request, positions,
+            (float*)out, n_tokens, n_head, n_kv_head, head_dim, v_dim, (const float*)gate, gate_stride, page_tokens,
+            max_pages, window, scale, num_pages, n_requests);
     MG_CHECK_LAUNCH("paged_attention_generic");
     return MG_OK;
+}
+
+// The same for a fused projection's rows [q | k | v] with keys and values of one size:
+// qkv: [n_tokens, (n_head + 2 n_kv_head) * head_dim]; out: [n_tokens, n_head * head_dim].
+MG_API int mg_paged_attention_generic(const void* qkv, const void* k_pages, const void* v_pages,
+                                      const int* block_table, const int* token_request,
+                                      const int* positions, void* out, int n_tokens, int n_head,
+                                      int n_kv_head, int head_dim, int page_tokens, int max_pages,
+                                      int window, float scale, int num_pages, int n_requests, int is_bf16,
+                                      void* stream) {
+    return mg_paged_attention_general(qkv, (n_head + 2 * n_kv_head) * head_dim, k_pages, v_pages, block_table,
+                                      token_request, positions, out, n_tokens, n_head, n_kv_head, head_dim, head_dim,
+                                      nullptr, 0, page_tokens, max_pages, window, scale, num_pages, n_requests, is_bf16,
+                                      stream);
 }

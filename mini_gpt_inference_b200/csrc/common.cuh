@@ -148,6 +148,12 @@ __device__ __forceinline__ float gelu_tanh(float u) {
     return 0.5f * u * (1.0f + tanhf(k * (u + 0.044715f * u * u * u)));
 }
 
+// The square of the positive part: max(u, 0)^2.
+__device__ __forceinline__ float relu_sq(float u) {
+    const float r = fmaxf(u, 0.f);
+    return r * r;
+}
+
 // tanh-GELU with the hardware's tanh (one instruction, relative error about 2^-11): for results that
 // are rounded to bfloat16 (2^-8) right away, where the exact tanhf costs twenty times the instructions.
 __device__ __forceinline__ float gelu_tanh_fast(float u) {

@@ -4,7 +4,7 @@
 MG_GUARD_DECLARE(elementwise)
 
 // ---- embedding + learned position add ---------------------------------------------------
-// x[n, :] = tok_emb[id[n], :] + pos_emb[pos[n], :]   (32-bit out; pos_emb may be null)
+// x[n, :] = tok_emb[id[n], :] * scale + pos_emb[pos[n], :]   (32-bit out; pos_emb may be null)
 // A row with a negative position is padding of a fixed-size batch: it becomes zeros.
 // With `source` given, a row whose source[n] >= 0 takes its id from previous[source[n]] (the token
 // the step before sampled, still on the device) instead of ids[n].
@@ -12,7 +12,8 @@ template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict__ pos,
                              const TW* __restrict__ tok, const TW* __restrict__ ptab,
                              float* __restrict__ out, int width, const int* __restrict__ source,
-                             const int* __restrict__ previous, int vocab, int n_positions, int n_previous) {
+                             const int* __restrict__ previous, int vocab, int n_positions, int n_previous,
+                             float scale) {
     const int n = blockIdx.x;
     float* orow = out + (size_t)n * width;
     int p = pos[n];
@@ -31,7 +32,7 @@ __global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict_
     const TW* trow = tok + (size_t)id * width;
     const TW* prow = ptab ? ptab + (size_t)p * width : nullptr;
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
-        float v = to_float(trow[c]);
+        float v = to_float(trow[c]) * scale;
         if (prow) v += to_float(prow[c]);
         orow[c] = v;
     }
@@ -41,7 +42,7 @@ __global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict_
 // are held against in guarded builds).
 MG_API int mg_embed(const int* ids, const int* pos, const void* tok, const void* ptab, float* out,
                     int n_tokens, int width, int weights_bf16, const int* source, const int* previous,
-                    int vocab, int n_positions, int n_previous, void* stream) {
+                    int vocab, int n_positions, int n_previous, float scale, void* stream) {
     if (n_tokens == 0) return MG_OK;
     MG_REQUIRE(n_tokens > 0 && width > 0 && vocab > 0, "embed: bad sizes");
     MG_REQUIRE(source == nullptr || previous != nullptr, "embed: token sources without the ids they point to");
@@ -49,10 +50,10 @@ MG_API int mg_embed(const int* ids, const int* pos, const void* tok, const void*
     int threads = width >= 256 ? 256 : 128;
     if (weights_bf16)
         embed_kernel<bf16><<<n_tokens, threads, 0, s>>>(ids, pos, (const bf16*)tok, (const bf16*)ptab, out, width, source,
-                                                       previous, vocab, n_positions, n_previous);
+                                                       previous, vocab, n_positions, n_previous, scale);
     else
         embed_kernel<float><<<n_tokens, threads, 0, s>>>(ids, pos, (const float*)tok, (const float*)ptab, out, width,
-                                                        source, previous, vocab, n_positions, n_previous);
+                                                        source, previous, vocab, n_positions, n_previous, scale);
     MG_CHECK_LAUNCH("embed");
     return MG_OK;
 }
@@ -266,5 +267,22 @@ MG_API int mg_zero_fill(void* dst, long long bytes, void* stream) {
                                      (uint4*)dst, n16, (uint8_t*)dst + n16 * 16, tail);
     if (le != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "zero_fill: %s", cudaGetErrorString(le));
     MG_CHECK_LAUNCH("zero_fill");
+    return MG_OK;
+}
+
+// ---- x *= scale, 32-bit, in place (logits of a head with an output scale) ---------------------------
+__global__ void scale_kernel(float* x, long long n, float scale) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] *= scale;
+}
+
+MG_API int mg_scale(float* x, long long n, float scale, void* stream) {
+    if (n == 0) return MG_OK;
+    MG_REQUIRE(n > 0 && n < (1ll << 40), "scale: bad size");
+    const cudaError_t e = mg_launch(scale_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (cudaStream_t)stream,
+                                    true, x, n, scale);
+    if (e != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "scale: %s", cudaGetErrorString(e));
     return MG_OK;
 }

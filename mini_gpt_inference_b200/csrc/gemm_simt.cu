@@ -10,6 +10,7 @@
 #define EPI_STORE 0      // out = acc + bias                (TOut)
 #define EPI_GELU 1       // out = gelu_tanh(acc + bias)     (TOut)
 #define EPI_RESIDUAL 2   // residual += acc + bias          (32-bit, in place)
+#define EPI_RELU_SQ 3    // out = max(acc + bias, 0)^2      (TOut)
 
 namespace {
 
@@ -66,6 +67,7 @@ gemm_simt_kernel(const TIn* __restrict__ a, const TIn* __restrict__ w, const flo
             float v = acc[i][j] + (bias ? bias[n] : 0.f);
             const size_t idx = (size_t)m * N + n;
             if (EPI == EPI_GELU) v = gelu_tanh(v);
+            if (EPI == EPI_RELU_SQ) v = relu_sq(v);
             if (EPI == EPI_RESIDUAL)
                 residual[idx] += v;
             else
@@ -84,6 +86,7 @@ int launch(const void* a, const void* w, const float* bias, void* out, float* re
     switch (epilogue) {
         case EPI_STORE: gemm_simt_kernel<TIn, TOut, EPI_STORE><<<grid, block, 0, s>>>(ap, wp, bias, op, residual, M, N, K); break;
         case EPI_GELU: gemm_simt_kernel<TIn, TOut, EPI_GELU><<<grid, block, 0, s>>>(ap, wp, bias, op, residual, M, N, K); break;
+        case EPI_RELU_SQ: gemm_simt_kernel<TIn, TOut, EPI_RELU_SQ><<<grid, block, 0, s>>>(ap, wp, bias, op, residual, M, N, K); break;
         case EPI_RESIDUAL: gemm_simt_kernel<TIn, TOut, EPI_RESIDUAL><<<grid, block, 0, s>>>(ap, wp, bias, op, residual, M, N, K); break;
         default: return mg_set_error(MG_ERR_ARG, "linear: unknown epilogue %d", epilogue);
     }

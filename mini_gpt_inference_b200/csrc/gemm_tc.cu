@@ -37,6 +37,7 @@ MG_GUARD_DECLARE(linear_tc)
 
 #define EPI_STORE 0
 #define EPI_GELU 1
+#define EPI_RELU_SQ 3
 #define EPI_RESIDUAL 2
 
 namespace {
@@ -238,6 +239,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                                 for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
                             }
                         }
+                        if (epilogue == EPI_RELU_SQ) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = relu_sq(v[j]);
+                        }
                         if (epilogue == EPI_RESIDUAL) {
                             // all loads first, then the adds and stores: a load after a store to the
                             // same array cannot be moved up by the compiler, and eight dependent
@@ -298,6 +303,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                             if (q < rows_q) {
                                 float v = __uint_as_float(r[j]) + bias_tile[c0 + j];
                                 if (epilogue == EPI_GELU) v = gelu_tanh(v);
+                                if (epilogue == EPI_RELU_SQ) v = relu_sq(v);
                                 if (epilogue == EPI_RESIDUAL) residual[row + q] += v;
                                 else if (out_bf16) {
                                     const bf16 hv = __float2bfloat16_rn(v);
@@ -329,6 +335,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                         if (q < rows_q) {
                             float v = __uint_as_float(r[j]) + b;
                             if (epilogue == EPI_GELU) v = gelu_tanh(v);
+                                if (epilogue == EPI_RELU_SQ) v = relu_sq(v);
                             const size_t idx = (size_t)q * ld_out + p;
                             if (epilogue == EPI_RESIDUAL) residual[idx] = old[j] + v;
                             else if (out_bf16) ((bf16*)out_ptr)[idx] = __float2bfloat16_rn(v);

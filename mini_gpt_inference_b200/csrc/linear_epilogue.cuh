@@ -8,6 +8,7 @@
 #define EPI_STORE 0
 #define EPI_GELU 1
 #define EPI_RESIDUAL 2
+#define EPI_RELU_SQ 3     // out = max(acc + bias, 0)^2
 
 struct LinearEpilogue {
     const float* bias;               // may be null
@@ -30,6 +31,7 @@ MG_GUARD_RECORD(linear_index_fault)
 __device__ __forceinline__ void linear_finish(const LinearEpilogue& e, int m, int n, float v, bool have_res, float res,
                                               bool have_slot = false, int slot_in = -1) {
     if (e.epilogue == EPI_GELU) v = gelu_tanh(v);
+    if (e.epilogue == EPI_RELU_SQ) v = relu_sq(v);
     const size_t idx = (size_t)m * e.N + n;
     if (e.epilogue == EPI_RESIDUAL) {
         e.residual[idx] = (have_res ? res : e.residual[idx]) + v;

@@ -1,0 +1,370 @@
+// A feed-forward of routed experts: router, grouping of the tokens by expert, the experts' two
+// matrix products over the groups, and the weighted sum back into the residual stream.
+//
+//   route:   z = W_r h (32-bit), the `top` largest z choose experts (ties: the lower index), their
+//            weights are softmax over the chosen z alone; optionally g = sigmoid(w_g . h), one number
+//            per token (the gate of an expert that every token uses).
+//   group:   entry (token, k) -> a slot; the slots of one expert are contiguous and in entry order.
+//   experts: H[slot] = silu(W_gate[e] h) * (W_up[e] h);  Y[slot] = weight[slot] * W_down[e] H[slot]  (32-bit)
+//   combine: x[token] += sum_k Y[slot of (token, k)], k in order: the same sum whatever the grouping.
+//
+// Nothing here depends on the host knowing how many tokens an expert got: grids are sized for the
+// worst case and blocks without work leave at once, so the whole part can sit in a CUDA graph.  Every
+// output element sums its terms in one fixed order (k = 0, 1, 2, ...), whatever else is in the batch.
+#include <math.h>
+
+#include "common.cuh"
+
+MG_GUARD_DECLARE(moe)
+
+namespace {
+
+// ---- router ------------------------------------------------------------------------------------
+constexpr int ROUTE_WARPS = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(32 * ROUTE_WARPS)
+moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w_router, const float* __restrict__ w_gate,
+                 const int* __restrict__ positions, int* __restrict__ ids, float* __restrict__ weights,
+                 float* __restrict__ gate, int n_tokens, int width, int n_experts, int top) {
+    extern __shared__ float z_smem[];                      // [ROUTE_WARPS][n_experts]
+    pdl_trigger();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int token = blockIdx.x * ROUTE_WARPS + warp;
+    if (token >= n_tokens) return;
+    if (positions != nullptr && positions[token] < 0) {    // padding of a fixed-size batch: no expert
+        for (int k = lane; k < top; k += 32) {
+            ids[(size_t)token * top + k] = -1;
+            weights[(size_t)token * top + k] = 0.f;
+        }
+        if (gate != nullptr && lane == 0) gate[token] = 0.f;
+        return;
+    }
+    float* z = z_smem + warp * n_experts;
+    const T* row = h + (size_t)token * width;
+    for (int e = 0; e < n_experts; ++e) {
+        const float* wr = w_router + (size_t)e * width;
+        float dot = 0.f;
+        for (int c = lane; c < width; c += 32) dot = fmaf(to_float(row[c]), wr[c], dot);
+        dot = warp_sum(dot);
+        if (lane == 0) z[e] = dot;
+    }
+    if (gate != nullptr) {
+        float dot = 0.f;
+        for (int c = lane; c < width; c += 32) dot = fmaf(to_float(row[c]), w_gate[c], dot);
+        dot = warp_sum(dot);
+        if (lane == 0) gate[token] = 1.0f / (1.0f + expf(-dot));
+    }
+    __syncwarp();
+    // the `top` largest, one after the other; every lane looks at a share of the experts
+    float z_max = 0.f, sum = 0.f;
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int best_e = 0x7fffffff;
+        for (int e = lane; e < n_experts; e += 32) {
+            const float v = z[e];
+            if (v > best || (v == best && e < best_e)) best = v, best_e = e;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (ov > best || (ov == best && oe < best_e)) best = ov, best_e = oe;
+        }
+        if (k == 0) z_max = best;
+        const float p = expf(best - z_max);
+        sum += p;
+        if (lane == 0) {
+            ids[(size_t)token * top + k] = best_e;
+            weights[(size_t)token * top + k] = p;
+            z[best_e] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    const float inv = 1.0f / sum;
+    for (int k = lane; k < top; k += 32) weights[(size_t)token * top + k] *= inv;
+}
+
+// ---- grouping -----------------------------------------------------------------------------------
+// Block e finds the entries that chose expert e: offsets[e] = entries that chose a lower expert,
+// and each of its entries gets slot offsets[e] + (its rank among them, in entry order).
+constexpr int SORT_THREADS = 256;
+
+__global__ void __launch_bounds__(SORT_THREADS)
+moe_group_kernel(const int* __restrict__ ids, int n_entries, int n_experts, int* __restrict__ offsets,
+                 int* __restrict__ slot_entry, int* __restrict__ entry_slot) {
+    __shared__ int warp_count[SORT_THREADS / 32];
+    __shared__ int total_less, total_equal, base;
+    pdl_trigger();
+    pdl_wait();
+    const int e = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) total_less = 0, total_equal = 0, base = 0;
+    __syncthreads();
+    int less = 0, equal = 0;
+    for (int i = tid; i < n_entries; i += SORT_THREADS) {
+        const int id = ids[i];
+        less += (id >= 0 && id < e);
+        equal += (id == e);
+    }
+    less = __reduce_add_sync(0xffffffffu, less);
+    equal = __reduce_add_sync(0xffffffffu, equal);
+    if (lane == 0) atomicAdd(&total_less, less), atomicAdd(&total_equal, equal);
+    __syncthreads();
+    const int first = total_less;
+    if (tid == 0) {
+        offsets[e] = first;
+        if (e == n_experts - 1) offsets[n_experts] = first + total_equal;
+    }
+    for (int i0 = 0; i0 < n_entries; i0 += SORT_THREADS) {
+        const int i = i0 + tid;
+        const int id = i < n_entries ? ids[i] : -1;
+        const bool mine = id == e;
+        const unsigned ballot = __ballot_sync(0xffffffffu, mine);
+        if (lane == 0) warp_count[warp] = __popc(ballot);
+        __syncthreads();
+        int before = base;
+        for (int w = 0; w < warp; ++w) before += warp_count[w];
+        if (mine) {
+            const int slot = first + before + __popc(ballot & ((1u << lane) - 1u));
+            slot_entry[slot] = i;
+            entry_slot[i] = slot;
+        } else if (e == 0 && i < n_entries && (id < 0 || id >= n_experts)) {
+            entry_slot[i] = -1;                            // an entry of a padding row
+        }
+        __syncthreads();
+        if (tid == 0) {
+            int add = 0;
+            for (int w = 0; w < SORT_THREADS / 32; ++w) add += warp_count[w];
+            base += add;
+        }
+        __syncthreads();
+    }
+}
+
+// ---- the experts' matrix products over the groups ------------------------------------------------
+// Tiles of 64 slots x 64 outputs, 16 of K at a time, on the CUDA cores (any sizes).  blockIdx.z is
+// the expert, blockIdx.y the tile of its slots (tiles beyond its count leave at once).
+constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
+
+__device__ __forceinline__ float silu(float z) { return z / (1.0f + expf(-z)); }
+
+// GLU = true:  out[slot, n] = silu(a . w[e][n]) * (a . w[e][inner + n]),  a = x[token of slot]   (T out)
+// GLU = false: out[slot, n] = scale[entry of slot] * (a . w[e][n]),       a = x[slot]            (32-bit out)
+template <typename T, bool GLU>
+__global__ void __launch_bounds__(256)
+moe_gemm_kernel(const T* __restrict__ x, int ldx, const T* __restrict__ w, long long w_expert_stride,
+                const int* __restrict__ offsets, const int* __restrict__ slot_entry, int top,
+                const float* __restrict__ scale, void* __restrict__ out, int N, int K, int x_rows) {
+    __shared__ float as[BK][BM + 4];
+    __shared__ float ws[BK][BN + 4];
+    __shared__ float us[GLU ? BK : 1][BN + 4];
+    __shared__ int row_of[BM];
+    pdl_trigger();
+    pdl_wait();
+    const int e = blockIdx.z;
+    const int first = offsets[e], count = offsets[e + 1] - first;
+    const int m0 = blockIdx.y * BM;
+    if (m0 >= count) return;
+    const int n0 = blockIdx.x * BN;
+    const int tid = threadIdx.x;
+    if (tid < BM) {
+        int r = -1;
+        if (m0 + tid < count) {
+            const int slot = first + m0 + tid;
+            r = GLU ? slot_entry[slot] / top : slot;
+            if (!MG_GUARDED(moe, MG_GUARD_ROW, r, x_rows)) r = -1;
+        }
+        row_of[tid] = r;
+    }
+    __syncthreads();
+    const T* we = w + (size_t)e * w_expert_stride;
+    const int tr = tid / 16, tc = tid % 16;
+    float acc[TM][TN], acc_u[GLU ? TM : 1][GLU ? TN : 1];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+            acc[i][j] = 0.f;
+            if constexpr (GLU) acc_u[i][j] = 0.f;
+        }
+    const int lrow = tid >> 2, lk = (tid & 3) * 4;
+    const int arow = row_of[lrow];
+    for (int k0 = 0; k0 < K; k0 += BK) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int k = k0 + lk + i;
+            const int n = n0 + lrow;
+            as[lk + i][lrow] = (arow >= 0 && k < K) ? to_float(x[(size_t)arow * ldx + k]) : 0.f;
+            ws[lk + i][lrow] = (n < N && k < K) ? to_float(we[(size_t)n * K + k]) : 0.f;
+            if constexpr (GLU) us[lk + i][lrow] = (n < N && k < K) ? to_float(we[(size_t)(N + n) * K + k]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < BK; ++k) {
+            float av[TM], wv[TN], uv[TN];
+#pragma unroll
+            for (int i = 0; i < TM; ++i) av[i] = as[k][tr * TM + i];
+#pragma unroll
+            for (int j = 0; j < TN; ++j) {
+                wv[j] = ws[k][tc * TN + j];
+                if constexpr (GLU) uv[j] = us[k][tc * TN + j];
+            }
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) {
+                    acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+                    if constexpr (GLU) acc_u[i][j] = fmaf(av[i], uv[j], acc_u[i][j]);
+                }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const int m = m0 + tr * TM + i;
+        if (m >= count) continue;
+        const size_t slot = (size_t)first + m;
+        const float sc = GLU ? 1.f : scale[slot_entry[slot]];
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+            const int n = n0 + tc * TN + j;
+            if (n >= N) continue;
+            if constexpr (GLU)
+                reinterpret_cast<T*>(out)[slot * N + n] = from_float<T>(silu(acc[i][j]) * acc_u[i][j]);
+            else
+                reinterpret_cast<float*>(out)[slot * N + n] = acc[i][j] * sc;
+        }
+    }
+}
+
+// ---- x[token] += sum over the token's entries, in entry order ----------------------------------
+__global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ entry_slot, int top,
+                                   float* __restrict__ residual, int width, int n_slots) {
+    pdl_trigger();
+    pdl_wait();
+    const int token = blockIdx.x;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float sum = 0.f;
+        for (int k = 0; k < top; ++k) {
+            const int slot = entry_slot[(size_t)token * top + k];
+            if (slot >= 0 && MG_GUARDED(moe, MG_GUARD_ROW, slot, n_slots)) sum += y[(size_t)slot * width + c];
+        }
+        residual[(size_t)token * width + c] += sum;
+    }
+}
+
+// ---- out[n, j] = silu(gu[n, j]) * gu[n, inner + j] (* scale[n]) -----------------------------------
+template <typename T>
+__global__ void glu_kernel(const T* __restrict__ gu, const float* __restrict__ scale, T* __restrict__ out, int rows,
+                           int inner) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)rows * inner) return;
+    const int n = (int)(i / inner), j = (int)(i - (long long)n * inner);
+    const float g = to_float(gu[(size_t)n * 2 * inner + j]), u = to_float(gu[(size_t)n * 2 * inner + inner + j]);
+    float v = silu(g) * u;
+    if (scale != nullptr) v *= scale[n];
+    out[i] = from_float<T>(v);
+}
+
+#define MG_LAUNCHED(e, name)                                                                 \
+    do {                                                                                     \
+        if ((e) != cudaSuccess) return mg_set_error(MG_ERR_CUDA, name ": %s", cudaGetErrorString(e)); \
+    } while (0)
+
+}  // namespace
+
+// h: [n_tokens, width] (bfloat16 if is_bf16 else 32-bit); w_router: [n_experts, width] and w_gate:
+// [width] (null: no gate), 32-bit; positions: [n_tokens] or null; ids, weights: [n_tokens, top];
+// gate: [n_tokens] or null.
+MG_API int mg_moe_route(const void* h, const float* w_router, const float* w_gate, const int* positions, int* ids,
+                        float* weights, float* gate, int n_tokens, int width, int n_experts, int top, int is_bf16,
+                        void* stream) {
+    if (n_tokens == 0) return MG_OK;
+    MG_REQUIRE(n_tokens > 0 && width > 0 && n_experts > 0 && top > 0 && top <= n_experts, "moe route: bad sizes");
+    MG_REQUIRE((w_gate == nullptr) == (gate == nullptr), "moe route: a gate wants its weights and its output");
+    const size_t smem = (size_t)ROUTE_WARPS * n_experts * sizeof(float);
+    MG_REQUIRE(smem <= 48 * 1024, "moe route: too many experts (%d)", n_experts);
+    const dim3 grid(ceil_div(n_tokens, ROUTE_WARPS)), block(32 * ROUTE_WARPS);
+    cudaError_t e;
+    if (is_bf16)
+        e = mg_launch(moe_route_kernel<bf16>, grid, block, smem, (cudaStream_t)stream, true, (const bf16*)h, w_router,
+                      w_gate, positions, ids, weights, gate, n_tokens, width, n_experts, top);
+    else
+        e = mg_launch(moe_route_kernel<float>, grid, block, smem, (cudaStream_t)stream, true, (const float*)h, w_router,
+                      w_gate, positions, ids, weights, gate, n_tokens, width, n_experts, top);
+    MG_LAUNCHED(e, "moe route");
+    return MG_OK;
+}
+
+// ids: [n_entries] chosen experts (-1: none); offsets: [n_experts + 1]; slot_entry, entry_slot: [n_entries].
+MG_API int mg_moe_group(const int* ids, int n_entries, int n_experts, int* offsets, int* slot_entry, int* entry_slot,
+                        void* stream) {
+    if (n_entries == 0) return MG_OK;
+    MG_REQUIRE(n_entries > 0 && n_entries < (1 << 24) && n_experts > 0, "moe group: bad sizes");
+    const cudaError_t e = mg_launch(moe_group_kernel, dim3(n_experts), dim3(SORT_THREADS), 0, (cudaStream_t)stream, true,
+                                    ids, n_entries, n_experts, offsets, slot_entry, entry_slot);
+    MG_LAUNCHED(e, "moe group");
+    return MG_OK;
+}
+
+// glu = 1: x [x_rows, ldx] gathered by token, w [n_experts, 2 N, K], out [n_entries, N] in the inputs' type.
+// glu = 0: x [n_entries, ldx] by slot, w [n_experts, N, K], scale [n_entries] by entry, out [n_entries, N] 32-bit.
+// max_rows: the most slots one expert can have (the tokens of the step).
+MG_API int mg_moe_gemm(const void* x, int ldx, const void* w, const int* offsets, const int* slot_entry, int top,
+                       const float* scale, void* out, int n_experts, int max_rows, int N, int K, int x_rows, int glu,
+                       int is_bf16, void* stream) {
+    if (max_rows == 0) return MG_OK;
+    MG_REQUIRE(n_experts > 0 && n_experts <= 65535 && max_rows > 0 && N > 0 && K > 0 && ldx >= K && top > 0,
+               "moe gemm: bad sizes");
+    MG_REQUIRE(glu || scale != nullptr, "moe gemm: the second product wants the entries' weights");
+    const dim3 grid(ceil_div(N, BN), ceil_div(max_rows, BM), n_experts), block(256);
+    MG_REQUIRE(grid.y <= 65535, "moe gemm: too many rows");
+    const long long stride = (long long)(glu ? 2 : 1) * N * K;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e;
+    if (is_bf16 && glu)
+        e = mg_launch(moe_gemm_kernel<bf16, true>, grid, block, 0, s, true, (const bf16*)x, ldx, (const bf16*)w, stride,
+                      offsets, slot_entry, top, scale, out, N, K, x_rows);
+    else if (is_bf16)
+        e = mg_launch(moe_gemm_kernel<bf16, false>, grid, block, 0, s, true, (const bf16*)x, ldx, (const bf16*)w, stride,
+                      offsets, slot_entry, top, scale, out, N, K, x_rows);
+    else if (glu)
+        e = mg_launch(moe_gemm_kernel<float, true>, grid, block, 0, s, true, (const float*)x, ldx, (const float*)w, stride,
+                      offsets, slot_entry, top, scale, out, N, K, x_rows);
+    else
+        e = mg_launch(moe_gemm_kernel<float, false>, grid, block, 0, s, true, (const float*)x, ldx, (const float*)w,
+                      stride, offsets, slot_entry, top, scale, out, N, K, x_rows);
+    MG_LAUNCHED(e, "moe gemm");
+    return MG_OK;
+}
+
+// y: [n_slots, width] 32-bit; entry_slot: [n_tokens, top] (-1: none); residual: [n_tokens, width] 32-bit.
+MG_API int mg_moe_combine(const float* y, const int* entry_slot, int top, float* residual, int n_tokens, int width,
+                          int n_slots, void* stream) {
+    if (n_tokens == 0) return MG_OK;
+    MG_REQUIRE(n_tokens > 0 && width > 0 && top > 0, "moe combine: bad sizes");
+    const cudaError_t e = mg_launch(moe_combine_kernel, dim3(n_tokens), dim3(width >= 256 ? 256 : 128), 0,
+                                    (cudaStream_t)stream, true, y, entry_slot, top, residual, width, n_slots);
+    MG_LAUNCHED(e, "moe combine");
+    return MG_OK;
+}
+
+// gu: [rows, 2 inner] (gate columns first); scale: [rows] 32-bit or null; out: [rows, inner].
+MG_API int mg_glu(const void* gu, const float* scale, void* out, int rows, int inner, int is_bf16, void* stream) {
+    if (rows == 0) return MG_OK;
+    MG_REQUIRE(rows > 0 && inner > 0, "glu: bad sizes");
+    const long long n = (long long)rows * inner;
+    const dim3 grid((unsigned)((n + 255) / 256)), block(256);
+    cudaError_t e;
+    if (is_bf16)
+        e = mg_launch(glu_kernel<bf16>, grid, block, 0, (cudaStream_t)stream, true, (const bf16*)gu, scale, (bf16*)out,
+                      rows, inner);
+    else
+        e = mg_launch(glu_kernel<float>, grid, block, 0, (cudaStream_t)stream, true, (const float*)gu, scale, (float*)out,
+                      rows, inner);
+    MG_LAUNCHED(e, "glu");
+    return MG_OK;
+}

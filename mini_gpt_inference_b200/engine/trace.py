@@ -21,7 +21,7 @@ import sys
 from pathlib import Path
 
 PAGE_ROUND = 64      # default of --page-round
-LIVE_REQUESTS = 8    # default of --live-requests
+LIVE_REQUESTS = 4    # default of --live-requests
 
 
 def parse_args(argv=None):
@@ -37,7 +37,7 @@ def parse_args(argv=None):
                     help="the multiple to which --max-tokens counts each request rounded up "
                          "(a multiple of --page-tokens; default 64)")
     ap.add_argument("--live-requests", type=int, default=LIVE_REQUESTS,
-                    help="most requests that are live at a time (state slots; default 8)")
+                    help="most requests that are live at a time (state slots; default 4)")
     ap.add_argument("--device", default="cuda:0")
     return ap.parse_args(argv)
 

@@ -17,7 +17,7 @@ from . import library
 from .attention_plan import KEY_CHUNK, query_tiles
 from .library import KernelLibraryError, check
 
-EPILOGUES = {"none": 0, "gelu_tanh": 1, "residual": 2}
+EPILOGUES = {"none": 0, "gelu_tanh": 1, "residual": 2, "relu_sq": 3}
 SKINNY_ROWS = 16         # most tokens the small-batch projection kernel takes
 CLUSTER_ROWS = 128       # most tokens the mid-batch (K split over a cluster) projection kernel takes
 CLUSTER_WIDE_MAX_BYTES = 3 << 20   # ... and the largest matrix it is given for more than 64 tokens
@@ -213,9 +213,9 @@ class CudaOps:
             raise KernelLibraryError(f"a kernel gave up waiting (code {code}); its results are invalid")
 
     # ---- embedding and norms --------------------------------------------------------------------
-    def embed(self, token_ids, positions, tok_emb, pos_table, source=None, previous=None):
-        """Rows of the embedding (plus rows of the position table).  With ``source``: a row whose
-        source is >= 0 takes its id from ``previous[source]`` instead of ``token_ids``."""
+    def embed(self, token_ids, positions, tok_emb, pos_table, source=None, previous=None, scale=1.0):
+        """Rows of the embedding times ``scale`` (plus rows of the position table).  With ``source``:
+        a row whose source is >= 0 takes its id from ``previous[source]`` instead of ``token_ids``."""
         self._want(token_ids, torch.int32, "token_ids", 1)
         self._want(positions, torch.int32, "positions", 1)
         if source is not None:
@@ -233,7 +233,7 @@ class CudaOps:
         self._run(self.lib.mg_embed(_ptr(token_ids), _ptr(positions), _ptr(tok_emb), _ptr(pos_table),
                                 _ptr(out), n, width, self._is_bf16(tok_emb), _ptr(source), _ptr(previous),
                                 tok_emb.shape[0], pos_table.shape[0] if pos_table is not None else 0,
-                                previous.numel() if previous is not None else 0, self._stream()),
+                                previous.numel() if previous is not None else 0, float(scale), self._stream()),
               "embed")
         return out
 
@@ -431,7 +431,7 @@ class CudaOps:
         return False
 
     def linear(self, x, weight, bias, activation, out_dtype):
-        if activation not in ("none", "gelu_tanh"):
+        if activation not in ("none", "gelu_tanh", "relu_sq"):
             raise KernelLibraryError(f"linear: no epilogue for activation {activation!r}")
         out = torch.empty((x.shape[0], weight.shape[0]), dtype=out_dtype, device=self.device)
         self._linear(x, weight, bias, EPILOGUES[activation], out, None)
@@ -527,16 +527,27 @@ class CudaOps:
         self.linear_residual(h, proj_weight, proj_bias, residual32)
         return residual32
 
-    def logits(self, y, tok_emb, greedy_out=None, vocab_limit=None):
-        """Logits in 32-bit.  With ``greedy_out`` (int32 ``[rows]``): the argmax of every row (ids at
-        or above ``vocab_limit`` excluded) is left there as well; returns ``(logits, taken)`` then,
-        ``taken`` False if the projection that ran cannot take it on its way."""
+    def scale_(self, x32, scale: float):
+        """``x32 *= scale`` in place (32-bit)."""
+        self._want(x32, torch.float32, "scale input")
+        self._run(self.lib.mg_scale(_ptr(x32), x32.numel(), float(scale), self._stream()), "scale")
+        return x32
+
+    def logits(self, y, tok_emb, greedy_out=None, vocab_limit=None, scale=1.0):
+        """Logits in 32-bit, times ``scale``.  With ``greedy_out`` (int32 ``[rows]``): the argmax of
+        every row (ids at or above ``vocab_limit`` excluded) is left there as well; returns
+        ``(logits, taken)`` then, ``taken`` False if the projection that ran cannot take it on its
+        way (a scale that is not positive would turn the order around: then it never does)."""
         if greedy_out is None:
-            return self.linear(y, tok_emb, None, "none", torch.float32)
+            out = self.linear(y, tok_emb, None, "none", torch.float32)
+            return out if scale == 1.0 else self.scale_(out, scale)
         self._ids_out(greedy_out, y.shape[0])
         out = torch.empty((y.shape[0], tok_emb.shape[0]), dtype=torch.float32, device=self.device)
         self.greedy_taken = False
-        self._linear(y, tok_emb, None, EPILOGUES["none"], out, None, greedy=(greedy_out, vocab_limit))
+        self._linear(y, tok_emb, None, EPILOGUES["none"], out, None,
+                     greedy=(greedy_out, vocab_limit) if scale > 0 else None)
+        if scale != 1.0:
+            self.scale_(out, scale)
         return out, self.greedy_taken
 
     # ---- attention ------------------------------------------------------------------------------
@@ -636,6 +647,126 @@ class CudaOps:
             _ptr(ctx.token_request), _ptr(ctx.positions), _ptr(out), n, n_head, n_kv_head, head_dim,
             cache.page_tokens, table.shape[1], window, float(scale), cache.k_pages.shape[0], table.shape[0],
             self._is_bf16(qkv), self._stream()), "paged_attention")
+        return out
+
+    def head_prepare(self, proj, n_head, n_kv_head, head_dim, v_dim, q_off, k_off, v_off, unit_norm, eps,
+                     cache, slots, positions, v_other=None, blend=None):
+        """Between a fused projection and the attention, in one kernel: query and key heads of
+        ``proj`` rows divided by their root mean square (``unit_norm``; queries in place), values
+        blended with ``v_other`` (a 2-D view whose rows' first columns are the other values of the
+        same tokens; ``blend`` a 32-bit scalar on the device), keys and values written to the cache
+        rows ``slots`` (``cache`` None or read-only: nothing is written)."""
+        self._want(proj, None, "projection rows", 2)
+        is_bf16 = self._is_bf16(proj)
+        args_other = [None, 0, None]
+        if v_other is not None:
+            if (v_other.dtype != proj.dtype or v_other.dim() != 2 or v_other.stride(1) != 1
+                    or v_other.shape[0] != proj.shape[0] or v_other.shape[1] < n_kv_head * v_dim):
+                raise KernelLibraryError("head_prepare: the other values do not fit the rows")
+            self._want(blend, torch.float32, "blend weight")
+            args_other = [_ptr(v_other), v_other.stride(0), _ptr(blend)]
+        pages = [None, None, None, 0, 0]
+        if cache is not None and cache.writes:
+            self._want(slots, torch.int32, "slot_mapping", 1)
+            self._want(cache.k_pages, proj.dtype, "k_pages", 4)
+            self._want(cache.v_pages, proj.dtype, "v_pages", 4)
+            if (tuple(cache.k_pages.shape[1:]) != (n_kv_head, cache.page_tokens, head_dim)
+                    or tuple(cache.v_pages.shape[1:]) != (n_kv_head, cache.page_tokens, v_dim)):
+                raise KernelLibraryError("head_prepare: page storage does not match the head sizes")
+            pages = [_ptr(slots), _ptr(cache.k_pages), _ptr(cache.v_pages), cache.page_tokens, cache.k_pages.shape[0]]
+        self._run(self.lib.mg_head_prepare(
+            _ptr(proj), proj.shape[1], proj.shape[0], n_head, n_kv_head, head_dim, v_dim, q_off, k_off, v_off,
+            1 if unit_norm else 0, float(eps), *args_other, pages[0], _ptr(positions), pages[1], pages[2],
+            pages[3], pages[4], is_bf16, self._stream()), "head_prepare")
+
+    def paged_attention_general(self, q, n_head, n_kv_head, head_dim, v_dim, scale, cache, ctx, gate=None):
+        """Causal attention of ``q`` (a 2-D tensor whose rows' first ``n_head * head_dim`` columns
+        are the queries) over the pages, keys of size ``head_dim`` and values of size ``v_dim``;
+        with ``gate`` (a 2-D view, ``n_head * v_dim`` columns) the output is multiplied by the
+        logistic function of the gate values.  Returns ``[tokens, n_head * v_dim]``."""
+        self._want(q, cache.k_pages.dtype, "queries", 2)
+        table = self._want(ctx.block_tables[cache.group], torch.int32, "block_table", 2)
+        n = q.shape[0]
+        if gate is not None and (gate.dtype != q.dtype or gate.dim() != 2 or gate.stride(1) != 1
+                                 or gate.shape != (n, n_head * v_dim)):
+            raise KernelLibraryError("attention: the gate does not fit the heads")
+        out = torch.empty((n, n_head * v_dim), dtype=q.dtype, device=self.device)
+        self._run(self.lib.mg_paged_attention_general(
+            _ptr(q), q.shape[1], _ptr(cache.k_pages), _ptr(cache.v_pages), _ptr(table), _ptr(ctx.token_request),
+            _ptr(ctx.positions), _ptr(out), n, n_head, n_kv_head, head_dim, v_dim, _ptr(gate),
+            gate.stride(0) if gate is not None else 0, cache.page_tokens, table.shape[1], int(cache.window or 0),
+            float(scale), cache.k_pages.shape[0], table.shape[0], self._is_bf16(q), self._stream()),
+            "paged_attention (general)")
+        return out
+
+    # ---- routed experts ---------------------------------------------------------------------------
+    def moe_route(self, y, router_weight, gate_weight, positions, top):
+        """Router of a feed-forward of experts: returns (ids [tokens, top] int32, weights [tokens,
+        top] 32-bit, gate [tokens] 32-bit or None): the ``top`` largest of ``router_weight @ y``
+        with the softmax over them, and the logistic function of ``gate_weight . y``."""
+        self._want(y, None, "router input", 2)
+        self._want(router_weight, torch.float32, "router weight", 2)
+        n, width = y.shape
+        experts = router_weight.shape[0]
+        if router_weight.shape[1] != width or not 0 < top <= experts:
+            raise KernelLibraryError("moe_route: shapes do not fit")
+        ids = torch.empty((n, top), dtype=torch.int32, device=self.device)
+        weights = torch.empty((n, top), dtype=torch.float32, device=self.device)
+        gate = None
+        if gate_weight is not None:
+            self._want(gate_weight, torch.float32, "gate weight")
+            if gate_weight.numel() != width:
+                raise KernelLibraryError("moe_route: the gate's weights do not fit the width")
+            gate = torch.empty((n,), dtype=torch.float32, device=self.device)
+        self._run(self.lib.mg_moe_route(_ptr(y), _ptr(router_weight), _ptr(gate_weight), _ptr(positions), _ptr(ids),
+                                        _ptr(weights), _ptr(gate), n, width, experts, top, self._is_bf16(y),
+                                        self._stream()), "moe route")
+        return ids, weights, gate
+
+    def moe_experts_residual(self, y, ids, weights, w_in, w_out, residual32):
+        """``residual32[t] += sum_k weights[t, k] * expert(ids[t, k])(y[t])`` with expert e as
+        ``w_out[e] @ (silu(w_in[e][:F] @ y) * (w_in[e][F:] @ y))``; ``w_in`` [E, 2F, C], ``w_out``
+        [E, C, F].  Tokens are grouped by expert on the device; the host never learns the counts."""
+        self._want(y, w_in.dtype, "expert input", 2)
+        self._want(w_in, None, "expert matrices (in)", 3)
+        self._want(w_out, w_in.dtype, "expert matrices (out)", 3)
+        self._want(residual32, torch.float32, "residual", 2)
+        n, width = y.shape
+        experts, two_f, _ = w_in.shape
+        inner, top = two_f // 2, ids.shape[1]
+        if (w_in.shape != (experts, 2 * inner, width) or w_out.shape != (experts, width, inner)
+                or ids.shape[0] != n or weights.shape != ids.shape or residual32.shape != (n, width)):
+            raise KernelLibraryError("moe_experts: shapes do not fit")
+        entries = n * top
+        is_bf16 = self._is_bf16(y)
+        offsets = torch.empty((experts + 1,), dtype=torch.int32, device=self.device)
+        slot_entry = torch.empty((entries,), dtype=torch.int32, device=self.device)
+        entry_slot = torch.empty((entries,), dtype=torch.int32, device=self.device)
+        self._run(self.lib.mg_moe_group(_ptr(ids), entries, experts, _ptr(offsets), _ptr(slot_entry), _ptr(entry_slot),
+                                        self._stream()), "moe group")
+        hidden = torch.empty((entries, inner), dtype=y.dtype, device=self.device)
+        self._run(self.lib.mg_moe_gemm(_ptr(y), width, _ptr(w_in), _ptr(offsets), _ptr(slot_entry), top, None,
+                                       _ptr(hidden), experts, n, inner, width, n, 1, is_bf16, self._stream()),
+                  "moe experts (in)")
+        out = torch.empty((entries, width), dtype=torch.float32, device=self.device)
+        self._run(self.lib.mg_moe_gemm(_ptr(hidden), inner, _ptr(w_out), _ptr(offsets), _ptr(slot_entry), top,
+                                       _ptr(weights), _ptr(out), experts, n, width, inner, entries, 0, is_bf16,
+                                       self._stream()), "moe experts (out)")
+        self._run(self.lib.mg_moe_combine(_ptr(out), _ptr(entry_slot), top, _ptr(residual32), n, width, entries,
+                                          self._stream()), "moe combine")
+
+    def glu(self, gate_up, row_scale=None):
+        """``silu(gate_up[:, :F]) * gate_up[:, F:]``, each row times ``row_scale`` (32-bit ``[rows]``)
+        if given; the result has the input's dtype."""
+        self._want(gate_up, None, "gate and up features", 2)
+        rows, two_f = gate_up.shape
+        if two_f % 2:
+            raise KernelLibraryError("glu: an odd number of columns")
+        if row_scale is not None and self._want(row_scale, torch.float32, "row scale", 1).numel() != rows:
+            raise KernelLibraryError("glu: one scale per row")
+        out = torch.empty((rows, two_f // 2), dtype=gate_up.dtype, device=self.device)
+        self._run(self.lib.mg_glu(_ptr(gate_up), _ptr(row_scale), _ptr(out), rows, two_f // 2, self._is_bf16(gate_up),
+                                  self._stream()), "glu")
         return out
 
     # ---- sampling -------------------------------------------------------------------------------

@@ -1,4 +1,4 @@
-from . import attention, block, embedding, layernorm, mlp, positions  # noqa: F401  (register)
+from . import attention, block, embedding, gated_attention, layernorm, mlp, moe, positions  # noqa: F401  (register)
 from .base import (ARRANGEMENTS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS,
                    POSITION_ENCODINGS, FeedForward, Mixer, Norm, Part, PositionEncoding,
                    register_arrangement, register_embedding, register_feed_forward,

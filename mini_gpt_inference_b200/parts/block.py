@@ -8,6 +8,7 @@ nothing), or into another tensor that they return (a kernel that fuses the whole
 always write where it reads); an arrangement hands the stream on with ``stream_after`` and
 returns the tensor that holds it at the end (or nothing, if that is the one it was given).
 ``pre_norm``: ``x += mixer(norm1(x)); x += ff(norm2(x))`` (src/minigpt_infer/model.py:112-115).
+``pre_norm_mixer_only``: ``x += mixer(norm1(x))``, for a layer without a feed-forward.
 """
 
 from __future__ import annotations
@@ -70,3 +71,12 @@ def pre_norm(ctx, layer: Layer, cache, residual32):
 
 pre_norm.requires = ("norm1", "mixer", "norm2", "feed_forward")
 register_arrangement("pre_norm")(pre_norm)
+
+
+def pre_norm_mixer_only(ctx, layer: Layer, cache, residual32):
+    x = residual32
+    return stream_after(layer.mixer.forward(ctx, cache, _normed(ctx, layer.norm1, layer.mixer, x), x), x)
+
+
+pre_norm_mixer_only.requires = ("norm1", "mixer")
+register_arrangement("pre_norm_mixer_only")(pre_norm_mixer_only)

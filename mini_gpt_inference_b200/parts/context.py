@@ -70,6 +70,9 @@ class StepContext:
     logit_rows: torch.Tensor              # [W] rows whose logits are wanted
     # What parts planned for this step on the host (``Part.plan_step``): int32 tensors by name.
     extra: dict = field(default_factory=dict)
+    # What parts hand to later parts within one forward pass (a layer's values that later layers
+    # blend in, for instance), by name; emptied when a pass begins.
+    shared: dict = field(default_factory=dict)
     # Optional: where token_source[i] >= 0, token i is fed_ids[token_source[i]] (a token the step
     # before sampled, still on the device) instead of token_ids[i].
     token_source: torch.Tensor | None = None

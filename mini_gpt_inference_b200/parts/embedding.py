@@ -3,7 +3,10 @@ the output head that shares its matrix.
 
 ``x = tok_emb[id] + pos_emb[pos]`` into the 32-bit residual stream
 (src/minigpt_infer/model.py:183); ``logits = y @ tok_emb^T`` without bias, 32-bit out
-(src/minigpt_infer/model.py:128-130, 187).
+(src/minigpt_infer/model.py:128-130, 187).  Both take a scale (1 unless given):
+``x = scale * tok_emb[id] + ...`` and ``logits = scale * (y @ tok_emb^T)``; the head uses the
+table as stored, without the embedding's scale.  ``tensor_name`` names the table in the
+checkpoint where it is not ``<prefix>weight``.
 """
 
 from __future__ import annotations
@@ -19,21 +22,29 @@ class TokenEmbedding(Part):
     # before sampled); an embedding without this flag gets its tokens gathered by a kernel in front.
     takes_token_source = True
 
-    def __init__(self, prefix: str, vocab_size: int, width: int) -> None:
+    def __init__(self, prefix: str, vocab_size: int, width: int, scale: float = 1.0,
+                 tensor_name: str | None = None) -> None:
         super().__init__(prefix)
-        self.vocab_size, self.width = vocab_size, width
+        self.vocab_size, self.width, self.scale = vocab_size, width, float(scale)
+        self.tensor_name = tensor_name if tensor_name is not None else self.prefix + "weight"
         self.weight = None
 
     def tensor_specs(self):
-        return {self.prefix + "weight": TensorSpec((self.vocab_size, self.width), "matrix")}
+        return {self.tensor_name: TensorSpec((self.vocab_size, self.width), "matrix")}
+
+    def bind(self, tensors) -> None:
+        self.weight = tensors.get(self.tensor_name)
 
     def forward(self, ctx, position):
         table = position.table() if position is not None else None
         if getattr(ctx, "token_source", None) is not None:
             # some tokens are still on the device where the step before sampled them
             return ctx.ops.embed(ctx.token_ids, ctx.positions, self.weight, table,
-                                 source=ctx.token_source, previous=ctx.fed_ids)
-        return ctx.ops.embed(ctx.token_ids, ctx.positions, self.weight, table)
+                                 source=ctx.token_source, previous=ctx.fed_ids, **self._scale_arg())
+        return ctx.ops.embed(ctx.token_ids, ctx.positions, self.weight, table, **self._scale_arg())
+
+    def _scale_arg(self) -> dict:
+        return {} if self.scale == 1.0 else {"scale": self.scale}
 
 
 @register_head("tied_head")
@@ -44,12 +55,16 @@ class TiedHead(Part):
     under the head's own name; then it must equal the embedding."""
 
     def __init__(self, prefix: str, vocab_size: int, width: int, tied_to: str,
-                 embedding=None) -> None:
+                 embedding=None, scale: float = 1.0, stored_again: bool = True) -> None:
         super().__init__(prefix)
         self.vocab_size, self.width, self.tied_to = vocab_size, width, tied_to
         self.embedding = embedding
+        self.scale = float(scale)
+        self.stored_again = stored_again      # whether a checkpoint may repeat the table under the head's name
 
     def tensor_specs(self):
+        if not self.stored_again:
+            return {}
         return {self.prefix + "weight": TensorSpec((self.vocab_size, self.width), "matrix",
                                                    optional_alias_of=self.tied_to)}
 
@@ -63,6 +78,9 @@ class TiedHead(Part):
         if greedy_out is not None:
             # the step also wants each row's greedy choice: the projection may take it on its way
             logits, ctx.greedy_taken = ctx.ops.logits(y, self.embedding.weight, greedy_out,
-                                                      getattr(ctx, "greedy_vocab_limit", None))
+                                                      getattr(ctx, "greedy_vocab_limit", None), **self._scale_arg())
             return logits
-        return ctx.ops.logits(y, self.embedding.weight)
+        return ctx.ops.logits(y, self.embedding.weight, **self._scale_arg())
+
+    def _scale_arg(self) -> dict:
+        return {} if self.scale == 1.0 else {"scale": self.scale}

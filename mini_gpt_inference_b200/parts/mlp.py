@@ -2,7 +2,9 @@
 
 The reference's MLP (src/minigpt_infer/model.py:93-101) with its hidden width and its
 activation as parameters; ``gelu_tanh(u) = 0.5 u (1 + tanh(sqrt(2/pi) (u + 0.044715 u^3)))``
-is evaluated in 32-bit inside the first projection's epilogue.
+is evaluated in 32-bit inside the first projection's epilogue, and so is ``relu_sq(u) =
+max(u, 0)^2``.  ``fc_name`` and ``proj_name`` name the two matrices inside the part's prefix
+where they are not ``fc`` and ``proj`` (then without a ``.weight`` suffix).
 """
 
 from __future__ import annotations
@@ -10,7 +12,8 @@ from __future__ import annotations
 from .base import FeedForward, register_feed_forward
 from .spec import TensorSpec
 
-_ACTIVATIONS = {"gelu_tanh": "gelu_tanh", "gelu_new": "gelu_tanh", "gelu_pytorch_tanh": "gelu_tanh"}
+_ACTIVATIONS = {"gelu_tanh": "gelu_tanh", "gelu_new": "gelu_tanh", "gelu_pytorch_tanh": "gelu_tanh",
+                "relu_sq": "relu_sq", "relu2": "relu_sq"}
 
 
 @register_feed_forward("dense_mlp")
@@ -18,7 +21,8 @@ class DenseMLP(FeedForward):
     graph_safe = True      # launches kernels only; nothing is decided on the host per step
 
     def __init__(self, prefix: str, width: int, inner: int, bias: bool,
-                 activation: str = "gelu_tanh") -> None:
+                 activation: str = "gelu_tanh", fc_name: str | None = None,
+                 proj_name: str | None = None) -> None:
         super().__init__(prefix)
         if activation not in _ACTIVATIONS:
             raise ValueError(f"activation {activation!r} has no kernel epilogue; known: "
@@ -26,17 +30,28 @@ class DenseMLP(FeedForward):
         self.width, self.inner, self.has_bias = width, inner, bool(bias)
         self.activation = _ACTIVATIONS[activation]
         self.fc_weight = self.fc_bias = self.proj_weight = self.proj_bias = None
+        p = self.prefix
+        self._names = {
+            "fc_weight": p + (fc_name if fc_name is not None else "fc.weight"),
+            "proj_weight": p + (proj_name if proj_name is not None else "proj.weight"),
+            "fc_bias": p + (fc_name + ".bias" if fc_name is not None else "fc.bias"),
+            "proj_bias": p + (proj_name + ".bias" if proj_name is not None else "proj.bias"),
+        }
 
     def tensor_specs(self):
-        p = self.prefix
+        n = self._names
         specs = {
-            p + "fc.weight": TensorSpec((self.inner, self.width), "matrix"),
-            p + "proj.weight": TensorSpec((self.width, self.inner), "matrix", "residual_proj"),
+            n["fc_weight"]: TensorSpec((self.inner, self.width), "matrix"),
+            n["proj_weight"]: TensorSpec((self.width, self.inner), "matrix", "residual_proj"),
         }
         if self.has_bias:
-            specs[p + "fc.bias"] = TensorSpec((self.inner,), "vector", "bias")
-            specs[p + "proj.bias"] = TensorSpec((self.width,), "vector", "bias")
+            specs[n["fc_bias"]] = TensorSpec((self.inner,), "vector", "bias")
+            specs[n["proj_bias"]] = TensorSpec((self.width,), "vector", "bias")
         return specs
+
+    def bind(self, tensors) -> None:
+        for attr, name in self._names.items():
+            setattr(self, attr, tensors.get(name))
 
     accepts_deferred_norm = True
 

@@ -67,6 +67,8 @@ class DecoderModel:
     # ---- one step ------------------------------------------------------------------------
     def forward(self, ctx):
         """Run ``ctx``'s tokens; return 32-bit logits ``[len(ctx.logit_rows), vocab]``."""
+        if getattr(ctx, "shared", None) is not None:
+            ctx.shared.clear()
         x = self.embedding.forward(ctx, self.position)
         for call in self.layer_order:
             layer = self.layers[call.layer]

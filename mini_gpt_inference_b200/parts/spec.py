@@ -88,5 +88,6 @@ class TensorSpec:
     role: str = "matrix"        # "matrix": stored in the compute dtype; "vector": kept in 32-bit;
                                 # "table": integer table kept as int32
     init: str = "normal"        # random-weights mode: "normal" | "residual_proj" | "norm_gain" |
-                                # "norm_shift" | "bias"
+                                # "norm_shift" | "bias" | "unit_interval" (a number in 0..1)
     optional_alias_of: str | None = None   # e.g. lm_head.weight may repeat tok_emb.weight
+    optional: bool = False      # a checkpoint may hold it or not (a tensor the model never reads)

@@ -67,7 +67,7 @@ def check_and_bind(tensors: Mapping[str, torch.Tensor],
     bound: dict[str, torch.Tensor] = {}
     for name, spec in expected.items():
         if name not in tensors:
-            if spec.optional_alias_of is None:
+            if spec.optional_alias_of is None and not spec.optional:
                 missing.append(name)
             continue
         t = tensors[name]

@@ -29,7 +29,7 @@ def random_tensors(model: DecoderModel, seed: int, dtype: torch.dtype = torch.fl
     specs = model.tensor_specs()
     for name in sorted(specs):
         spec = specs[name]
-        if spec.optional_alias_of is not None:
+        if spec.optional_alias_of is not None or spec.optional:
             continue
         if spec.role == "table":
             out[name] = torch.randint(0, 2**15, spec.shape, generator=gen, dtype=torch.int32)
@@ -41,6 +41,8 @@ def random_tensors(model: DecoderModel, seed: int, dtype: torch.dtype = torch.fl
             t = 1.0 + 0.1 * noise
         elif spec.init == "norm_shift":
             t = 0.1 * noise
+        elif spec.init == "unit_interval":
+            t = torch.sigmoid(noise)
         else:  # "normal", "bias"
             t = 0.02 * noise
         out[name] = t.to(dtype)
