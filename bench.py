@@ -24,6 +24,11 @@ tokens each) through ``LLMEngine.generate``, wall clock: the scheduler's mixed b
 and one 2,048-token prompt (an event pair around every launch; the reference sums its kernels' time
 from a profiler's trace, bench/bench_kernels.py:71-116).
 
+``--only designs`` prints a line of its own: the Fakilorn decoder beside this decoder at equal width,
+depth, hidden width and vocabulary (random weights, two sizes): a 2,048-token prompt step, decode
+steps at the headline batch with contexts near 2,048, and the device time of every exported function
+in each.
+
 ``--sizes`` runs the same measurement at the layer sizes of GPT-2 small or GPT-2 XL (position
 table of 1,024: the prefill step is then two whole prompts of 1,024 tokens).
 
@@ -82,7 +87,7 @@ def parse_args():
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--page-tokens", type=int, default=64)
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and prefill")
-    ap.add_argument("--only", choices=["all", "decode", "prefill", "serve", "kernels"], default="all",
+    ap.add_argument("--only", choices=["all", "decode", "prefill", "serve", "kernels", "designs"], default="all",
                     help="a small case for profilers: only the device-timed decode steps, or only "
                          "the 2,048-token prefill (the printed line is then partial); serve: 64 "
                          "requests with prompts of 16 to 512 tokens and 256 generated tokens each "
@@ -437,6 +442,113 @@ def kernel_times(args) -> dict:
     return out
 
 
+# ``--only designs``: the Fakilorn decoder beside the GPT-2 style decoder at equal width, depth, hidden
+# width and vocabulary (random weights), prompt and decode steps with the device time of every
+# exported function.  key/value head sizes 64/64 (what the GPT-2 style attention kernels take too) and
+# 96/64 (keys larger than values, which only the general attention kernel serves).
+DESIGN_SIZES = {
+    "w1024": dict(width=1024, layers=4, heads=16, kv_heads=4, ff=4096, vocab=32000, experts=8, top=2, expert_ff=1024,
+                  shared_ff=1024),
+    "w2048": dict(width=2048, layers=2, heads=16, kv_heads=4, ff=8192, vocab=32000, experts=16, top=4, expert_ff=1024,
+                  shared_ff=2048),
+}
+
+
+def _fakilorn_raw(sz: dict, dim: int, vdim: int, moe: bool) -> dict:
+    mixer = {"heads": sz["heads"], "kv_heads": sz["kv_heads"], "dim": dim, "vdim": vdim, "scale": dim ** -0.5,
+             "v_mix": True}
+    dense = {"kind": "dense", "ff": sz["ff"]}
+    routed = {"kind": "moe", "expert": {"ff": sz["expert_ff"]}, "router": {"experts": sz["experts"], "top": sz["top"]},
+              "shared": {"ff": sz["shared_ff"]}}
+    layers = [{"type": "attention", "mixer": dict(mixer), "mlp": routed if (moe and i % 2) else dense}
+              for i in range(sz["layers"])]
+    return {"architecture": "Fakilorn", "vocab": sz["vocab"], "width": sz["width"], "layers": layers,
+            "embedding": {"scale": 1.0}, "logit_scale": 1.0, "norm": {"eps": 1e-5}}
+
+
+def compare_designs(args) -> dict:
+    import torch
+
+    from mini_gpt_inference_b200 import FakilornConfig, GPTConfig
+    from mini_gpt_inference_b200.config import lookup
+    from mini_gpt_inference_b200.engine.build import load_model, make_runner
+    from mini_gpt_inference_b200.engine.runner import StepEntry
+    from mini_gpt_inference_b200.kernels.ops import default_ops
+    from mini_gpt_inference_b200.kernels.timing import LaunchTimer
+    from mini_gpt_inference_b200.parts import DecoderModel
+    from mini_gpt_inference_b200.weights import random_tensors
+
+    ops = default_ops("cuda:0")
+    batch, context, prompt_len = args.batch, 2048, PREFILL_TOKENS
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda:0")
+    out = {"impl": "ours", "partial": "designs side by side", "dtype": args.dtype, "batch": batch, "context": context,
+           "prompt": prompt_len, "rows": []}
+
+    def measure(name, cfg):
+        model = DecoderModel(lookup(cfg.architecture).describe(cfg))
+        store = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
+        loaded = load_model(config=cfg, tensors=random_tensors(model, 0, store), dtype=args.dtype, device="cuda:0")
+        pt = args.page_tokens
+        runner = make_runner(loaded, ops, pt, (batch + 1) * (context // pt + 2), batch + 1)
+        gen = torch.Generator().manual_seed(1)
+        vocab = cfg.vocab_size
+
+        def prompt(n):
+            return torch.randint(0, vocab, (n,), generator=gen).tolist()
+
+        def timed(fn, reps):
+            times = []
+            for rep in range(reps + 3):
+                flush.zero_()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                fn()
+                b.record()
+                torch.cuda.synchronize()
+                if rep >= 3:
+                    times.append(a.elapsed_time(b))
+            return statistics.median(times)
+
+        def one_prompt():
+            runner.step([StepEntry("p", prompt(prompt_len), [prompt_len - 1])])
+            runner.finish("p")
+
+        row = {"model": name, "parameters_m": round(cfg.num_parameters() / 1e6, 1)}
+        pre_ms = timed(one_prompt, 5)
+        row["prefill_ms"] = round(pre_ms, 3)
+        row["prefill_tok_s"] = round(prompt_len / (pre_ms * 1e-3))
+        rids = [f"d{i}" for i in range(batch)]
+        for rid in rids:
+            runner.step([StepEntry(rid, prompt(context - 40), [])])
+        dec_ms = timed(lambda: runner.step([StepEntry(rid, [7], [0]) for rid in rids]), 24)
+        row["decode_ms_per_step"] = round(dec_ms, 4)
+        row["decode_tok_s"] = round(batch / (dec_ms * 1e-3))
+        runner.use_cuda_graphs = False
+        for what, fn in (("decode", lambda: runner.step([StepEntry(rid, [7], [0]) for rid in rids])), ("prefill", one_prompt)):
+            for rep in range(3):
+                with LaunchTimer(ops) as timer:
+                    fn()
+                rows = timer.summary()
+            row[what + "_functions"] = [{"function": r.name, "calls": r.calls, "total_us": round(r.total_us, 1),
+                                         "mean_us": round(r.mean_us, 2)} for r in rows]
+        for rid in rids:
+            runner.finish(rid)
+        ops.check_status()
+        del runner, loaded
+        torch.cuda.empty_cache()
+        return row
+
+    for size_name, sz in DESIGN_SIZES.items():
+        gpt = GPTConfig.from_dict(dict(vocab_size=sz["vocab"], n_positions=context + 64, n_layer=sz["layers"],
+                                       n_head=sz["heads"], n_embd=sz["width"], n_inner=sz["ff"], bias=False,
+                                       layer_norm_epsilon=1e-5))
+        out["rows"].append(measure(f"gpt2-style {size_name}", gpt))
+        for dim, vdim, moe in ((64, 64, False), (64, 64, True), (96, 64, True)):
+            cfg = FakilornConfig.from_dict(_fakilorn_raw(sz, dim, vdim, moe))
+            out["rows"].append(measure(f"fakilorn {size_name} heads {dim}/{vdim} {'dense+experts' if moe else 'dense'}", cfg))
+    return out
+
+
 def check_decode_logits(args) -> dict:
     """Outside every timed region: the decode step that the benchmark times (batch 8, contexts of
     2,048, the replayed graph) is run once on fixed tokens and its logits are compared with rows
@@ -496,6 +608,8 @@ def run_ours(args) -> dict:
         return serve_mixed(args)
     if args.only == "kernels":
         return kernel_times(args)
+    if args.only == "designs":
+        return compare_designs(args)
     if args.only == "decode":
         cfg, windows, launches, mean_ctx, clocks = device_decode(args, args.batch, args.steps, args.warmup,
                                                                  min_seconds=0.0)

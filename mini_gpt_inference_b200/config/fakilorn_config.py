@@ -170,6 +170,24 @@ class FakilornConfig:
                 "layers": [layer.to_dict() for layer in self.layers], "logit_scale": self.logit_scale,
                 "norm": {"eps": self.norm_eps}, "vocab": self.vocab, "width": self.width}
 
+    def num_parameters(self) -> int:
+        c = self.width
+        total = self.vocab * c + 2 * c
+        for layer in self.layers:
+            m = layer.mixer
+            total += 2 * c + c * (m.heads * m.dim + m.kv_heads * (m.dim + m.vdim) + 2 * m.heads * m.vdim)
+            total += 1 if m.v_mix else 0
+            f = layer.mlp
+            if f is None:
+                continue
+            total += 2 * c
+            if f.kind == "dense":
+                total += 2 * c * f.ff
+            else:
+                total += f.experts * (c + 3 * c * f.ff)
+                total += 0 if f.shared_ff is None else 3 * c * f.shared_ff + c
+        return total
+
     def save(self, model_dir: str | Path) -> Path:
         model_dir = Path(model_dir)
         model_dir.mkdir(parents=True, exist_ok=True)
