@@ -1,0 +1,479 @@
+// Causal attention over the paged cache on the warp-level tensor cores, for key and value heads of
+// different sizes, grouped query heads, a window and an output gate; bfloat16 in, 32-bit softmax.
+//
+// The rows of a tile are (token, query head of one key/value head's group) pairs; a CTA of four warps
+// walks blocks of 64 keys: keys and values of the block come from their pages into padded shared
+// memory, S = Q K^T by mma.sync m16n8k16 (Q fragments stay in registers), the running maximum, sum
+// and the weights in 32-bit, P rounded to bfloat16 as the A operand of O += P V (V through
+// ldmatrix.trans).  Head sizes are rounded up to a compiled size (64, 96 or 128 key features, 64 or
+// 128 value features); the padding is zeros in registers and shared memory.
+//
+//   tiles  (portions of prompts): a tile is 64 / group consecutive tokens of one request with all the
+//          group's heads, 16 rows per warp; every warp walks every key block.  The CTA finds its
+//          request and tile from the requests' token counts on the device.
+//   split  (single tokens): a CTA is one token, one key/value head and one range of keys; the
+//          group's heads are the rows of one m16 tile, each warp takes 16 of a block's 64 keys, the
+//          warps' partial results meet in shared memory and go to scratch; a second kernel merges
+//          the ranges, applies the gate and stores.
+//
+// Keys are always read from the pages, whichever step wrote them.  Rows of pages beyond a request's
+// last key are never multiplied into a result (their values are replaced by zeros in shared memory).
+#include <math.h>
+
+#include "common.cuh"
+
+MG_GUARD_DECLARE(attention_mma)
+
+namespace {
+
+constexpr int KB = 64;            // keys per block
+constexpr int PAD = 8;            // bfloat16 elements of padding per shared-memory row
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct AttnParams {
+    const bf16* q;                // rows of q_stride elements, heads of D
+    int q_stride;
+    const bf16* k_pages;          // [page, G, page_tokens, D]
+    const bf16* v_pages;          // [page, G, page_tokens, DV]
+    const int* block_table;       // [n_requests, max_pages]
+    const int* token_request;     // [n_tokens]
+    const int* positions;         // [n_tokens]
+    const int* req_q_start;       // [n_requests]
+    const int* req_q_len;         // [n_requests]
+    const bf16* gate;             // rows of gate_stride elements, heads of DV; may be null
+    int gate_stride;
+    bf16* out;                    // [n_tokens, H * DV]
+    float* part_o;                // split: [n_tokens, H, splits, DV]
+    float* part_ml;               // split: [n_tokens, H, splits, 2]
+    int n_tokens, n_requests, n_head, n_kv_head, d, dv, page_tokens, max_pages, window, num_pages;
+    int tile_tokens;              // tiles: tokens per tile
+    int splits, split_keys;       // split: ranges of keys per token
+    float scale_log2;             // scale * log2(e)
+};
+
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldsm4(uint32_t (&r)[4], const bf16* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldsm4_t(uint32_t (&r)[4], const bf16* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// Keys j0 .. j0+63 of one request and key/value head into shared memory: rows [KB][DP+PAD] and
+// [KB][DVP+PAD].  Rows outside lo..hi become zeros (they may hold anything in the pages).
+template <int DP, int DVP>
+__device__ __forceinline__ void load_block(const AttnParams& p, const int* table, int kv_head, int j0, int lo, int hi,
+                                           bf16* ks, bf16* vs, int tid, int threads) {
+    const int kc = p.d / 8, vc = p.dv / 8;               // 16-byte chunks per row
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    for (int i = tid; i < KB * (kc + vc); i += threads) {
+        const int key = i / (kc + vc), c = i - key * (kc + vc);
+        const int j = j0 + key;
+        uint4 v = zero;
+        if (j >= lo && j <= hi) {
+            int page = table[j / p.page_tokens];
+            if (!MG_GUARDED(attention_mma, MG_GUARD_PAGE, page, p.num_pages)) page = 0;
+            const size_t row = ((size_t)page * p.n_kv_head + kv_head) * p.page_tokens + (j % p.page_tokens);
+            v = c < kc ? *reinterpret_cast<const uint4*>(p.k_pages + row * p.d + c * 8)
+                       : *reinterpret_cast<const uint4*>(p.v_pages + row * p.dv + (c - kc) * 8);
+        }
+        if (c < kc) *reinterpret_cast<uint4*>(ks + key * (DP + PAD) + c * 8) = v;
+        else *reinterpret_cast<uint4*>(vs + key * (DVP + PAD) + (c - kc) * 8) = v;
+    }
+}
+
+// Zero the columns that the loads never write (head sizes below the compiled ones).
+template <int DP, int DVP>
+__device__ __forceinline__ void zero_padding(const AttnParams& p, bf16* ks, bf16* vs, int tid, int threads) {
+    const bf16 z = __float2bfloat16_rn(0.f);
+    if (p.d < DP)
+        for (int i = tid; i < KB * (DP - p.d); i += threads) ks[(i / (DP - p.d)) * (DP + PAD) + p.d + i % (DP - p.d)] = z;
+    if (p.dv < DVP)
+        for (int i = tid; i < KB * (DVP - p.dv); i += threads) vs[(i / (DVP - p.dv)) * (DVP + PAD) + p.dv + i % (DVP - p.dv)] = z;
+}
+
+// The query fragments of a lane's two rows (null pointer: zeros), columns beyond d as zeros.
+template <int DP>
+__device__ __forceinline__ void load_q(uint32_t (&qf)[DP / 16][4], const bf16* q0, const bf16* q1, int d, int lane) {
+    const int c = 2 * (lane & 3);
+#pragma unroll
+    for (int ks = 0; ks < DP / 16; ++ks) {
+        const int c0 = 16 * ks + c, c1 = c0 + 8;
+        qf[ks][0] = (q0 && c0 < d) ? *reinterpret_cast<const uint32_t*>(q0 + c0) : 0u;
+        qf[ks][1] = (q1 && c0 < d) ? *reinterpret_cast<const uint32_t*>(q1 + c0) : 0u;
+        qf[ks][2] = (q0 && c1 < d) ? *reinterpret_cast<const uint32_t*>(q0 + c1) : 0u;
+        qf[ks][3] = (q1 && c1 < d) ? *reinterpret_cast<const uint32_t*>(q1 + c1) : 0u;
+    }
+}
+
+// One warp, its 16 rows, NT * 8 keys of the block in shared memory starting at key `k_first`:
+// scores, masks, the running maximum and sum, and O += P V.  pos/lo: the two rows' own last and first
+// visible key (pos < 0: a row without a token).
+template <int DP, int DVP, int NT>
+__device__ __forceinline__ void attend(const uint32_t (&qf)[DP / 16][4], const bf16* ks, const bf16* vs, int k_first,
+                                       int j_first, const int (&pos)[2], const int (&lo)[2], float scale_log2,
+                                       float (&m)[2], float (&l)[2], float (&o)[DVP / 8][4], int lane) {
+    float s[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < DP / 16; ++kk) {
+#pragma unroll
+        for (int n = 0; n < NT; n += 2) {
+            uint32_t b[4];
+            ldsm4(b, ks + (k_first + n * 8 + (lane >> 4) * 8 + (lane & 7)) * (DP + PAD) + kk * 16 + ((lane >> 3) & 1) * 8);
+            mma16816(s[n], qf[kk], b[0], b[1]);
+            mma16816(s[n + 1], qf[kk], b[2], b[3]);
+        }
+    }
+    // masks and the block's maximum per row
+    float bm[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int j = j_first + n * 8 + 2 * (lane & 3) + (e & 1), r = e >> 1;
+            const float v = (j <= pos[r] && j >= lo[r]) ? s[n][e] * scale_log2 : -INFINITY;
+            s[n][e] = v;
+            bm[r] = fmaxf(bm[r], v);
+        }
+    float corr[2], base[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        bm[r] = fmaxf(bm[r], __shfl_xor_sync(0xffffffffu, bm[r], 1));
+        bm[r] = fmaxf(bm[r], __shfl_xor_sync(0xffffffffu, bm[r], 2));
+        const float nm = fmaxf(m[r], bm[r]);
+        corr[r] = (m[r] == -INFINITY) ? 0.f : exp2f(m[r] - nm);
+        base[r] = (nm == -INFINITY) ? 0.f : nm;            // a row that has seen no key yet: weights stay 0
+        m[r] = nm;
+    }
+    float bs[2] = {0.f, 0.f};
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float pr = exp2f(s[n][e] - base[e >> 1]);
+            s[n][e] = pr;
+            bs[e >> 1] += pr;
+        }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        bs[r] += __shfl_xor_sync(0xffffffffu, bs[r], 1);
+        bs[r] += __shfl_xor_sync(0xffffffffu, bs[r], 2);
+        l[r] = l[r] * corr[r] + bs[r];
+    }
+#pragma unroll
+    for (int n = 0; n < DVP / 8; ++n) {
+        o[n][0] *= corr[0];
+        o[n][1] *= corr[0];
+        o[n][2] *= corr[1];
+        o[n][3] *= corr[1];
+    }
+#pragma unroll
+    for (int kk = 0; kk < NT / 2; ++kk) {                  // 16 keys at a time
+        uint32_t a[4];
+        a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+        for (int n = 0; n < DVP / 8; n += 2) {
+            uint32_t b[4];
+            ldsm4_t(b, vs + (k_first + kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * (DVP + PAD) + n * 8 + (lane >> 4) * 8);
+            mma16816(o[n], a, b[0], b[1]);
+            mma16816(o[n + 1], a, b[2], b[3]);
+        }
+    }
+}
+
+__device__ __forceinline__ float logistic(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+// ---- portions of prompts ---------------------------------------------------------------------------
+template <int DP, int DVP>
+__global__ void __launch_bounds__(128)
+attention_tiles_kernel(const AttnParams p) {
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    bf16* ks = reinterpret_cast<bf16*>(smem_raw);
+    bf16* vs = ks + KB * (DP + PAD);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    zero_padding<DP, DVP>(p, ks, vs, tid, 128);
+    pdl_trigger();
+    pdl_wait();
+    // which request, which tile of it
+    int tile = blockIdx.x, request = 0;
+    for (; request < p.n_requests; ++request) {
+        const int tiles = (p.req_q_len[request] + p.tile_tokens - 1) / p.tile_tokens;
+        if (tile < tiles) break;
+        tile -= tiles;
+    }
+    if (request >= p.n_requests) return;
+    const int kv_head = blockIdx.y, group = p.n_head / p.n_kv_head;
+    const int first = p.req_q_start[request] + tile * p.tile_tokens;
+    const int count = min(p.tile_tokens, p.req_q_len[request] - tile * p.tile_tokens);
+    int hi = p.positions[first + count - 1], lo_tile = 0;
+    if (hi < 0) return;                                     // padding
+    if (!MG_GUARDED(attention_mma, MG_GUARD_POSITION, hi, (long long)p.max_pages * p.page_tokens)) hi = 0;
+    if (p.window > 0) lo_tile = max(0, p.positions[first] - p.window + 1);
+    const int* table = p.block_table + (size_t)request * p.max_pages;
+
+    // this lane's two rows
+    int pos[2], lo[2], token[2], head[2];
+    const bf16* qrow[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = warp * 16 + (lane >> 2) + 8 * r;
+        const int t = row / group;
+        const bool live = t < count;
+        token[r] = first + (live ? t : 0);
+        head[r] = kv_head * group + row % group;
+        pos[r] = live ? p.positions[token[r]] : -1;
+        lo[r] = (p.window > 0 && pos[r] >= 0) ? max(0, pos[r] - p.window + 1) : 0;
+        qrow[r] = live ? p.q + (size_t)token[r] * p.q_stride + (size_t)head[r] * p.d : nullptr;
+    }
+    uint32_t qf[DP / 16][4];
+    load_q<DP>(qf, qrow[0], qrow[1], p.d, lane);
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f}, o[DVP / 8][4];
+#pragma unroll
+    for (int n = 0; n < DVP / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    // the last key this warp's rows can see (rows are in token order)
+    const int warp_last_token = min(count - 1, (warp * 16 + 15) / group);
+    const int warp_hi = (warp * 16) / group < count ? p.positions[first + warp_last_token] : -1;
+
+    for (int j0 = (lo_tile / KB) * KB; j0 <= hi; j0 += KB) {
+        __syncthreads();                                    // the block before has been used
+        load_block<DP, DVP>(p, table, kv_head, j0, lo_tile, hi, ks, vs, tid, 128);
+        __syncthreads();
+        if (j0 <= warp_hi) attend<DP, DVP, 8>(qf, ks, vs, 0, j0, pos, lo, p.scale_log2, m, l, o, lane);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        if (pos[r] < 0) continue;
+        const float inv = l[r] > 0.f ? 1.0f / l[r] : 0.f;
+        bf16* orow = p.out + (size_t)token[r] * p.n_head * p.dv + (size_t)head[r] * p.dv;
+        const bf16* grow = p.gate ? p.gate + (size_t)token[r] * p.gate_stride + (size_t)head[r] * p.dv : nullptr;
+#pragma unroll
+        for (int n = 0; n < DVP / 8; ++n) {
+            const int c = n * 8 + 2 * (lane & 3);
+            if (c >= p.dv) continue;
+            float a = o[n][2 * r] * inv, b = o[n][2 * r + 1] * inv;
+            if (grow) {
+                const __nv_bfloat162 g = *reinterpret_cast<const __nv_bfloat162*>(grow + c);
+                a *= logistic(__bfloat162float(g.x));
+                b *= logistic(__bfloat162float(g.y));
+            }
+            *reinterpret_cast<uint32_t*>(orow + c) = pack_bf16(a, b);
+        }
+    }
+}
+
+// ---- single tokens, the keys cut into ranges ---------------------------------------------------------
+template <int DP, int DVP>
+__global__ void __launch_bounds__(128)
+attention_split_kernel(const AttnParams p) {
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    bf16* ks = reinterpret_cast<bf16*>(smem_raw);
+    bf16* vs = ks + KB * (DP + PAD);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    zero_padding<DP, DVP>(p, ks, vs, tid, 128);
+    pdl_trigger();
+    pdl_wait();
+    const int token = blockIdx.x, kv_head = blockIdx.y, split = blockIdx.z;
+    const int group = p.n_head / p.n_kv_head;
+    int position = p.positions[token];
+    const bool padding = position < 0;
+    if (!padding && !MG_GUARDED(attention_mma, MG_GUARD_POSITION, position, (long long)p.max_pages * p.page_tokens)) position = 0;
+    const int lo_row = (p.window > 0 && !padding) ? max(0, position - p.window + 1) : 0;
+    const int first = (lo_row / KB) * KB + split * p.split_keys;         // ranges start at the window's block
+    const int last = min(position, first + p.split_keys - 1);
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f}, o[DVP / 8][4];
+#pragma unroll
+    for (int n = 0; n < DVP / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    const int row0 = lane >> 2;                              // rows are the group's heads; row0 + 8 as well
+    if (!padding && first <= last) {
+        int request = p.token_request[token];
+        if (!MG_GUARDED(attention_mma, MG_GUARD_REQUEST, request, p.n_requests)) request = 0;
+        const int* table = p.block_table + (size_t)request * p.max_pages;
+        int pos[2], lo[2];
+        const bf16* qrow[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int row = row0 + 8 * r;
+            const bool live = row < group;
+            pos[r] = live ? position : -1;
+            lo[r] = lo_row;
+            qrow[r] = live ? p.q + (size_t)token * p.q_stride + (size_t)(kv_head * group + row) * p.d : nullptr;
+        }
+        uint32_t qf[DP / 16][4];
+        load_q<DP>(qf, qrow[0], qrow[1], p.d, lane);
+        for (int j0 = first; j0 <= last; j0 += KB) {
+            __syncthreads();
+            load_block<DP, DVP>(p, table, kv_head, j0, lo_row, last, ks, vs, tid, 128);
+            __syncthreads();
+            if (j0 + warp * 16 <= last)
+                attend<DP, DVP, 2>(qf, ks, vs, warp * 16, j0 + warp * 16, pos, lo, p.scale_log2, m, l, o, lane);
+        }
+    }
+    // the four warps' partial results meet in shared memory (after the last block has been used)
+    __syncthreads();
+    float* sm_ml = reinterpret_cast<float*>(smem_raw);               // [4][16][2]
+    float* sm_o = sm_ml + 4 * 16 * 2;                                 // [4][16][DVP]
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = row0 + 8 * r;
+        if ((lane & 3) == 0) {
+            sm_ml[(warp * 16 + row) * 2] = m[r];
+            sm_ml[(warp * 16 + row) * 2 + 1] = l[r];
+        }
+#pragma unroll
+        for (int n = 0; n < DVP / 8; ++n) {
+            const int c = n * 8 + 2 * (lane & 3);
+            sm_o[(warp * 16 + row) * DVP + c] = o[n][2 * r];
+            sm_o[(warp * 16 + row) * DVP + c + 1] = o[n][2 * r + 1];
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < group * p.dv; i += 128) {
+        const int row = i / p.dv, c = i - row * p.dv;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) mm = fmaxf(mm, sm_ml[(w * 16 + row) * 2]);
+        float sum = 0.f, acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = sm_ml[(w * 16 + row) * 2];
+            const float f = mw == -INFINITY ? 0.f : exp2f(mw - mm);
+            sum += f * sm_ml[(w * 16 + row) * 2 + 1];
+            acc += f * sm_o[(w * 16 + row) * DVP + c];
+        }
+        const size_t slot = ((size_t)token * p.n_head + kv_head * group + row) * p.splits + split;
+        p.part_o[slot * p.dv + c] = acc;
+        if (c == 0) {
+            p.part_ml[slot * 2] = mm;
+            p.part_ml[slot * 2 + 1] = sum;
+        }
+    }
+}
+
+// out[token, head] = (sum over ranges of 2^(m_s - M) O_s) / (sum of 2^(m_s - M) l_s), times the gate.
+__global__ void attention_merge_kernel(const AttnParams p) {
+    pdl_trigger();
+    pdl_wait();
+    const int token = blockIdx.x, head = blockIdx.y;
+    const size_t base = ((size_t)token * p.n_head + head) * p.splits;
+    bf16* orow = p.out + (size_t)token * p.n_head * p.dv + (size_t)head * p.dv;
+    if (p.positions[token] < 0) {
+        for (int c = threadIdx.x; c < p.dv; c += blockDim.x) orow[c] = __float2bfloat16_rn(0.f);
+        return;
+    }
+    float mm = -INFINITY;
+    for (int s = 0; s < p.splits; ++s) mm = fmaxf(mm, p.part_ml[(base + s) * 2]);
+    float sum = 0.f;
+    for (int s = 0; s < p.splits; ++s) {
+        const float ms = p.part_ml[(base + s) * 2];
+        if (ms != -INFINITY) sum += exp2f(ms - mm) * p.part_ml[(base + s) * 2 + 1];
+    }
+    const float inv = sum > 0.f ? 1.0f / sum : 0.f;
+    const bf16* grow = p.gate ? p.gate + (size_t)token * p.gate_stride + (size_t)head * p.dv : nullptr;
+    for (int c = threadIdx.x; c < p.dv; c += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < p.splits; ++s) {
+            const float ms = p.part_ml[(base + s) * 2];
+            if (ms != -INFINITY) acc += exp2f(ms - mm) * p.part_o[(base + s) * p.dv + c];
+        }
+        acc *= inv;
+        if (grow) acc *= logistic(__bfloat162float(grow[c]));
+        orow[c] = __float2bfloat16_rn(acc);
+    }
+}
+
+template <int DP, int DVP>
+int launch(const AttnParams& p, int single_tokens, int n_tiles, cudaStream_t s) {
+    size_t smem = (size_t)KB * (DP + PAD + DVP + PAD) * sizeof(bf16);
+    cudaError_t e;
+    if (single_tokens) {
+        const size_t meet = (size_t)(4 * 16 * 2 + 4 * 16 * DVP) * sizeof(float);
+        if (meet > smem) smem = meet;
+        e = cudaFuncSetAttribute(attention_split_kernel<DP, DVP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess)
+            e = mg_launch(attention_split_kernel<DP, DVP>, dim3(p.n_tokens, p.n_kv_head, p.splits), dim3(128), smem, s, true, p);
+        if (e == cudaSuccess)
+            e = mg_launch(attention_merge_kernel, dim3(p.n_tokens, p.n_head), dim3(p.dv >= 128 ? 128 : 64), 0, s, true, p);
+    } else {
+        e = cudaFuncSetAttribute(attention_tiles_kernel<DP, DVP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess)
+            e = mg_launch(attention_tiles_kernel<DP, DVP>, dim3(n_tiles, p.n_kv_head), dim3(128), smem, s, true, p);
+    }
+    if (e != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "attention (mma): %s", cudaGetErrorString(e));
+    return MG_OK;
+}
+
+}  // namespace
+
+// Ranges of keys per token for contexts of up to max_context keys, and the keys per range.
+MG_API int mg_attention_mma_split_keys(int max_context) {
+    int keys = 256;
+    while ((max_context + keys - 1) / keys > 64) keys *= 2;
+    return keys;
+}
+
+MG_API long long mg_attention_mma_scratch_floats(int n_tokens, int n_head, int dv, int splits) {
+    return (long long)n_tokens * n_head * splits * (dv + 2);
+}
+
+// q: [n_tokens, q_stride] bfloat16 (heads of d features first); pages as in the general kernel;
+// gate: rows of gate_stride elements or null; out: [n_tokens, n_head * dv] bfloat16.
+// single_tokens = 1: every token is alone in its request's step (splits ranges of split_keys keys,
+// scratch of mg_attention_mma_scratch_floats floats); 0: n_tiles tiles of tile_tokens tokens, found
+// from req_q_start / req_q_len.  Returns MG_ERR_UNSUPPORTED for sizes it does not take.
+MG_API int mg_attention_mma(const void* q, int q_stride, const void* k_pages, const void* v_pages, const int* block_table,
+                            const int* token_request, const int* positions, const int* req_q_start,
+                            const int* req_q_len, const void* gate, int gate_stride, void* out, float* scratch,
+                            int n_tokens, int n_requests, int n_head, int n_kv_head, int d, int dv, int page_tokens,
+                            int max_pages, int window, float scale, int num_pages, int single_tokens, int n_tiles,
+                            int tile_tokens, int splits, int split_keys, void* stream) {
+    if (n_tokens == 0) return MG_OK;
+    MG_REQUIRE(n_tokens > 0 && n_head > 0 && n_kv_head > 0 && n_head % n_kv_head == 0 && page_tokens > 0 && max_pages > 0,
+               "attention: bad sizes");
+    const int group = n_head / n_kv_head;
+    const bool aligned = d % 8 == 0 && dv % 8 == 0 && q_stride % 8 == 0 && (gate == nullptr || gate_stride % 2 == 0) &&
+                         ((uintptr_t)q % 16 == 0) && ((uintptr_t)k_pages % 16 == 0) && ((uintptr_t)v_pages % 16 == 0) &&
+                         ((uintptr_t)out % 4 == 0) && ((uintptr_t)gate % 4 == 0);
+    if (!aligned || d > 128 || dv > 128 || group > (single_tokens ? 16 : 64) || n_kv_head > 65535) return MG_ERR_UNSUPPORTED;
+    AttnParams p;
+    p.q = (const bf16*)q; p.q_stride = q_stride; p.k_pages = (const bf16*)k_pages; p.v_pages = (const bf16*)v_pages;
+    p.block_table = block_table; p.token_request = token_request; p.positions = positions;
+    p.req_q_start = req_q_start; p.req_q_len = req_q_len; p.gate = (const bf16*)gate; p.gate_stride = gate_stride;
+    p.out = (bf16*)out; p.part_o = nullptr; p.part_ml = nullptr;
+    p.n_tokens = n_tokens; p.n_requests = n_requests; p.n_head = n_head; p.n_kv_head = n_kv_head; p.d = d; p.dv = dv;
+    p.page_tokens = page_tokens; p.max_pages = max_pages; p.window = window > 0 ? window : 0; p.num_pages = num_pages;
+    p.tile_tokens = tile_tokens; p.splits = splits; p.split_keys = split_keys; p.scale_log2 = scale * LOG2E;
+    if (single_tokens) {
+        MG_REQUIRE(scratch != nullptr && splits > 0 && splits <= 65535 && split_keys > 0 && split_keys % KB == 0,
+                   "attention: the ranges of keys want scratch and sizes that are multiples of %d", KB);
+        p.part_o = scratch;
+        p.part_ml = scratch + (size_t)n_tokens * n_head * splits * dv;
+    } else {
+        MG_REQUIRE(req_q_start && req_q_len && n_tiles > 0 && tile_tokens > 0 && tile_tokens * group <= 64,
+                   "attention: tiles of up to 64 rows");
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    const int dp = d <= 64 ? 64 : d <= 96 ? 96 : 128, dvp = dv <= 64 ? 64 : 128;
+    if (dp == 64 && dvp == 64) return launch<64, 64>(p, single_tokens, n_tiles, s);
+    if (dp == 64) return launch<64, 128>(p, single_tokens, n_tiles, s);
+    if (dp == 96 && dvp == 64) return launch<96, 64>(p, single_tokens, n_tiles, s);
+    if (dp == 96) return launch<96, 128>(p, single_tokens, n_tiles, s);
+    if (dvp == 64) return launch<128, 64>(p, single_tokens, n_tiles, s);
+    return launch<128, 128>(p, single_tokens, n_tiles, s);
+}

@@ -26,6 +26,8 @@ _SIGNATURES = {
     "mg_head_prepare": [_P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P],
     "mg_paged_attention_general": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _I, _I, _I, _F,
                                    _I, _I, _I, _P],
+    "mg_attention_mma": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F,
+                         _I, _I, _I, _I, _I, _I, _P],
     "mg_moe_route": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "mg_moe_group": [_P, _I, _I, _P, _P, _P, _P],
     "mg_moe_gemm": [_P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
@@ -66,7 +68,7 @@ _SIGNATURES = {
 
 # exported readers of the kernel files' index guards: mg_<name>_index_fault(long long[4])
 GUARDED_FILES = ("elementwise", "linear_skinny", "linear_stream", "linear_wide", "linear_cluster", "linear_tc",
-                 "attention_generic", "attention_split", "attention_prefill", "head_prepare", "moe")
+                 "attention_generic", "attention_split", "attention_prefill", "head_prepare", "moe", "attention_mma")
 for _name in GUARDED_FILES:
     _SIGNATURES[f"mg_{_name}_index_fault"] = [_P]
 GUARD_CODES = {1: "token id", 2: "position", 3: "cache row", 4: "page", 5: "request", 6: "row", 7: "token source"}
@@ -112,6 +114,10 @@ def load(verbose: bool = True):
     lib.mg_attention_split_launches.restype = c_int
     lib.mg_mlp_pack_elements.argtypes = [c_int, c_int]
     lib.mg_mlp_pack_elements.restype = ctypes.c_longlong
+    lib.mg_attention_mma_split_keys.argtypes = [c_int]
+    lib.mg_attention_mma_split_keys.restype = c_int
+    lib.mg_attention_mma_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
+    lib.mg_attention_mma_scratch_floats.restype = ctypes.c_longlong
     lib.mg_attention_split_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
     lib.mg_attention_split_scratch_floats.restype = ctypes.c_longlong
     _lib = lib

@@ -42,12 +42,18 @@ def dev(t, dtype=None):
 
 
 class Ctx:
-    """The few fields of a step's context that the attention kernel reads."""
+    """The few fields of a step's context that the attention kernels read."""
 
-    def __init__(self, tables, token_request, positions):
+    def __init__(self, tables, token_request, positions, q_len, decode_only=False):
         self.block_tables = [dev(torch.tensor(tables, dtype=torch.int32))]
         self.token_request = dev(torch.tensor(token_request, dtype=torch.int32))
         self.positions = dev(torch.tensor(positions, dtype=torch.int32))
+        starts = [sum(q_len[:i]) for i in range(len(q_len))]
+        self.req_q_start = dev(torch.tensor(starts, dtype=torch.int32))
+        self.req_q_len = dev(torch.tensor(q_len, dtype=torch.int32))
+        self.host_q_len = list(q_len)
+        self.decode_only = decode_only
+        self.max_ctx_after = max(positions) + 1
 
 
 # ---- mechanisms alone ---------------------------------------------------------------------------
@@ -95,9 +101,11 @@ def test_unit_norm_blend_and_page_write(ops, dtype, heads, groups, d, dv):
         assert torch.isnan(rows[~written]).all() and not torch.isnan(rows[written]).any()
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("heads,groups,d,dv,pt", [(4, 2, 24, 16, 8), (3, 3, 32, 32, 16), (6, 1, 10, 70, 4)])
-def test_attention_far_key_gate_and_sizes(ops, dtype, heads, groups, d, dv, pt):
+@pytest.mark.parametrize("dtype,path", [("float32", "general"), ("bfloat16", "general"), ("bfloat16", "tiles"),
+                                        ("bfloat16", "ranges")])
+@pytest.mark.parametrize("heads,groups,d,dv,pt", [(4, 2, 24, 16, 8), (3, 3, 32, 32, 16), (6, 1, 10, 70, 4),
+                                                  (8, 2, 96, 64, 16), (16, 1, 128, 128, 32), (5, 5, 72, 104, 8)])
+def test_attention_far_key_gate_and_sizes(ops, dtype, path, heads, groups, d, dv, pt):
     """Two requests on scattered pages.  Every query is made to point at one key far back (or, for the
     second request, at the key of a page's last row): with a large scale nearly all weight lies
     there, so an attention that misses that key, a head's group or the gate is off by far."""
@@ -127,13 +135,21 @@ def test_attention_far_key_gate_and_sizes(ops, dtype, heads, groups, d, dv, pt):
             q[i, h] += 0.7 * k_all[r][j, h // (heads // groups)]
     gate = torch.randn(n, heads * dv, generator=gen)
     scale = 6.0 / math.sqrt(d)
-    q_rows = torch.cat([q.reshape(n, -1), torch.randn(n, 7, generator=gen)], dim=1).to(t)     # wider rows
-    gate_rows = torch.cat([torch.randn(n, 3, generator=gen), gate], dim=1).to(t)
+    q_rows = torch.cat([q.reshape(n, -1), torch.randn(n, 8, generator=gen)], dim=1).to(t)     # wider rows
+    gate_rows = torch.cat([torch.randn(n, 4, generator=gen), gate], dim=1).to(t)
     cache = PagedKVView(dev(k_pages, t), dev(v_pages, t), 0, pt, None, False)
-    ctx = Ctx(tables, [r for r, _ in rows], [p for _, p in rows])
+    ctx = Ctx(tables, [r for r, _ in rows], [p for _, p in rows], [5, 25], decode_only=path == "ranges")
     g_dev = dev(gate_rows)
-    got = ops.paged_attention_general(dev(q_rows), heads, groups, d, dv, scale, cache, ctx, gate=g_dev[:, 3:])
-    got_plain = ops.paged_attention_general(dev(q_rows), heads, groups, d, dv, scale, cache, ctx)
+    launches = ops.launches
+    ops.use_mma_attention = path != "general"
+    try:
+        got = ops.paged_attention_general(dev(q_rows), heads, groups, d, dv, scale, cache, ctx, gate=g_dev[:, 4:])
+        got_plain = ops.paged_attention_general(dev(q_rows), heads, groups, d, dv, scale, cache, ctx)
+    finally:
+        ops.use_mma_attention = True
+    if d % 8 == 0 and dv % 8 == 0:
+        # sizes that the tensor-core kernels take: they ran (ranges: two launches a call), or they were off
+        assert ops.launches - launches == {"general": 2, "tiles": 2, "ranges": 4}[path]
     want = torch.empty(n, heads, dv, dtype=torch.float64)
     peak = []
     for i, (r, p) in enumerate(rows):
@@ -146,7 +162,7 @@ def test_attention_far_key_gate_and_sizes(ops, dtype, heads, groups, d, dv, pt):
     assert min(peak) > 0.5                                   # the chosen key does carry the weight
     tol = 2e-5 if dtype == "float32" else 3e-2
     assert torch.allclose(got_plain.double().cpu(), want.view(n, -1), atol=tol, rtol=tol)
-    gated = want.view(n, -1) * torch.sigmoid(gate_rows[:, 3:].double())
+    gated = want.view(n, -1) * torch.sigmoid(gate_rows[:, 4:].double())
     assert torch.allclose(got.double().cpu(), gated, atol=tol, rtol=tol)
 
 
