@@ -3,7 +3,7 @@
 //
 // The rows of a tile are (token, query head of one key/value head's group) pairs; a CTA of four warps
 // walks blocks of 64 keys: keys and values of the block come from their pages into padded shared
-// memory, S = Q K^T by mma.sync m16n8k16 (Q fragments stay in registers), the running maximum, sum
+// memory (cp.async, two buffers in turn), S = Q K^T by mma.sync m16n8k16 (Q fragments stay in registers), the running maximum, sum
 // and the weights in 32-bit, P rounded to bfloat16 as the A operand of O += P V (V through
 // ldmatrix.trans).  Head sizes are rounded up to a compiled size (64, 96 or 128 key features, 64 or
 // 128 value features); the padding is zeros in registers and shared memory.
@@ -71,26 +71,34 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-// Keys j0 .. j0+63 of one request and key/value head into shared memory: rows [KB][DP+PAD] and
-// [KB][DVP+PAD].  Rows outside lo..hi become zeros (they may hold anything in the pages).
+// Keys j0 .. j0+63 of one request and key/value head into shared memory, asynchronously: rows
+// [KB][DP+PAD] and [KB][DVP+PAD].  Rows outside lo..hi become zeros (they may hold anything in the
+// pages).  The caller commits the group and waits for it.
+__device__ __forceinline__ void cp_async16(bf16* dst, const bf16* src, bool real) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    const int bytes = real ? 16 : 0;                       // 0: nothing is read, the 16 bytes become zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 template <int DP, int DVP>
 __device__ __forceinline__ void load_block(const AttnParams& p, const int* table, int kv_head, int j0, int lo, int hi,
                                            bf16* ks, bf16* vs, int tid, int threads) {
     const int kc = p.d / 8, vc = p.dv / 8;               // 16-byte chunks per row
-    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
     for (int i = tid; i < KB * (kc + vc); i += threads) {
         const int key = i / (kc + vc), c = i - key * (kc + vc);
         const int j = j0 + key;
-        uint4 v = zero;
-        if (j >= lo && j <= hi) {
+        const bool real = j >= lo && j <= hi;
+        size_t row = 0;
+        if (real) {
             int page = table[j / p.page_tokens];
             if (!MG_GUARDED(attention_mma, MG_GUARD_PAGE, page, p.num_pages)) page = 0;
-            const size_t row = ((size_t)page * p.n_kv_head + kv_head) * p.page_tokens + (j % p.page_tokens);
-            v = c < kc ? *reinterpret_cast<const uint4*>(p.k_pages + row * p.d + c * 8)
-                       : *reinterpret_cast<const uint4*>(p.v_pages + row * p.dv + (c - kc) * 8);
+            row = ((size_t)page * p.n_kv_head + kv_head) * p.page_tokens + (j % p.page_tokens);
         }
-        if (c < kc) *reinterpret_cast<uint4*>(ks + key * (DP + PAD) + c * 8) = v;
-        else *reinterpret_cast<uint4*>(vs + key * (DVP + PAD) + (c - kc) * 8) = v;
+        if (c < kc) cp_async16(ks + key * (DP + PAD) + c * 8, p.k_pages + row * p.d + c * 8, real);
+        else cp_async16(vs + key * (DVP + PAD) + (c - kc) * 8, p.v_pages + row * p.dv + (c - kc) * 8, real);
     }
 }
 
@@ -202,17 +210,20 @@ __device__ __forceinline__ float logistic(float x) { return 1.0f / (1.0f + expf(
 
 // ---- portions of prompts ---------------------------------------------------------------------------
 template <int DP, int DVP>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, (DP + DVP <= 128) ? 3 : ((DP + DVP <= 192) ? 2 : 1))
 attention_tiles_kernel(const AttnParams p) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
+    constexpr int STAGE = KB * (DP + PAD + DVP + PAD);     // elements of one buffer: keys, then values
     bf16* ks = reinterpret_cast<bf16*>(smem_raw);
     bf16* vs = ks + KB * (DP + PAD);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     zero_padding<DP, DVP>(p, ks, vs, tid, 128);
+    zero_padding<DP, DVP>(p, ks + STAGE, vs + STAGE, tid, 128);
     pdl_trigger();
     pdl_wait();
-    // which request, which tile of it
-    int tile = blockIdx.x, request = 0;
+    // which request, which tile of it; the grid's first CTAs take the last tiles, whose tokens see the
+    // most keys, so that the long ones do not start last
+    int tile = (int)(gridDim.x - 1 - blockIdx.x), request = 0;
     for (; request < p.n_requests; ++request) {
         const int tiles = (p.req_q_len[request] + p.tile_tokens - 1) / p.tile_tokens;
         if (tile < tiles) break;
@@ -251,11 +262,23 @@ attention_tiles_kernel(const AttnParams p) {
     const int warp_last_token = min(count - 1, (warp * 16 + 15) / group);
     const int warp_hi = (warp * 16) / group < count ? p.positions[first + warp_last_token] : -1;
 
-    for (int j0 = (lo_tile / KB) * KB; j0 <= hi; j0 += KB) {
-        __syncthreads();                                    // the block before has been used
-        load_block<DP, DVP>(p, table, kv_head, j0, lo_tile, hi, ks, vs, tid, 128);
+    // two buffers take turns: the next block's copies are in flight while this one is multiplied
+    const int j_begin = (lo_tile / KB) * KB;
+    load_block<DP, DVP>(p, table, kv_head, j_begin, lo_tile, hi, ks, vs, tid, 128);
+    cp_async_commit();
+    int buf = 0;
+    for (int j0 = j_begin; j0 <= hi; j0 += KB, buf ^= 1) {
+        if (j0 + KB <= hi) {
+            load_block<DP, DVP>(p, table, kv_head, j0 + KB, lo_tile, hi, ks + (buf ^ 1) * STAGE, vs + (buf ^ 1) * STAGE, tid, 128);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
         __syncthreads();
-        if (j0 <= warp_hi) attend<DP, DVP, 8>(qf, ks, vs, 0, j0, pos, lo, p.scale_log2, m, l, o, lane);
+        if (j0 <= warp_hi)
+            attend<DP, DVP, 8>(qf, ks + buf * STAGE, vs + buf * STAGE, 0, j0, pos, lo, p.scale_log2, m, l, o, lane);
+        __syncthreads();                                    // the buffer is free for the block after the next
     }
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
@@ -283,10 +306,12 @@ template <int DP, int DVP>
 __global__ void __launch_bounds__(128)
 attention_split_kernel(const AttnParams p) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
+    constexpr int STAGE = KB * (DP + PAD + DVP + PAD);     // elements of one buffer: keys, then values
     bf16* ks = reinterpret_cast<bf16*>(smem_raw);
     bf16* vs = ks + KB * (DP + PAD);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     zero_padding<DP, DVP>(p, ks, vs, tid, 128);
+    zero_padding<DP, DVP>(p, ks + STAGE, vs + STAGE, tid, 128);
     pdl_trigger();
     pdl_wait();
     const int token = blockIdx.x, kv_head = blockIdx.y, split = blockIdx.z;
@@ -317,12 +342,22 @@ attention_split_kernel(const AttnParams p) {
         }
         uint32_t qf[DP / 16][4];
         load_q<DP>(qf, qrow[0], qrow[1], p.d, lane);
-        for (int j0 = first; j0 <= last; j0 += KB) {
-            __syncthreads();
-            load_block<DP, DVP>(p, table, kv_head, j0, lo_row, last, ks, vs, tid, 128);
+        load_block<DP, DVP>(p, table, kv_head, first, lo_row, last, ks, vs, tid, 128);
+        cp_async_commit();
+        int buf = 0;
+        for (int j0 = first; j0 <= last; j0 += KB, buf ^= 1) {
+            if (j0 + KB <= last) {
+                load_block<DP, DVP>(p, table, kv_head, j0 + KB, lo_row, last, ks + (buf ^ 1) * STAGE, vs + (buf ^ 1) * STAGE, tid, 128);
+                cp_async_commit();
+                cp_async_wait<1>();
+            } else {
+                cp_async_wait<0>();
+            }
             __syncthreads();
             if (j0 + warp * 16 <= last)
-                attend<DP, DVP, 2>(qf, ks, vs, warp * 16, j0 + warp * 16, pos, lo, p.scale_log2, m, l, o, lane);
+                attend<DP, DVP, 2>(qf, ks + buf * STAGE, vs + buf * STAGE, warp * 16, j0 + warp * 16, pos, lo, p.scale_log2, m, l,
+                                   o, lane);
+            __syncthreads();
         }
     }
     // the four warps' partial results meet in shared memory (after the last block has been used)
@@ -400,7 +435,7 @@ __global__ void attention_merge_kernel(const AttnParams p) {
 
 template <int DP, int DVP>
 int launch(const AttnParams& p, int single_tokens, int n_tiles, cudaStream_t s) {
-    size_t smem = (size_t)KB * (DP + PAD + DVP + PAD) * sizeof(bf16);
+    size_t smem = (size_t)2 * KB * (DP + PAD + DVP + PAD) * sizeof(bf16);      // two buffers
     cudaError_t e;
     if (single_tokens) {
         const size_t meet = (size_t)(4 * 16 * 2 + 4 * 16 * DVP) * sizeof(float);

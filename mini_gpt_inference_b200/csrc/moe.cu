@@ -20,43 +20,59 @@ MG_GUARD_DECLARE(moe)
 namespace {
 
 // ---- router ------------------------------------------------------------------------------------
-constexpr int ROUTE_WARPS = 4;
+// One CTA per token: its warps share the experts (and the gate, as one more row of weights), a lane
+// sums every 32nd group of four features in a fixed order, so a token's logits depend on nothing
+// but the token.  Warp 0 then picks the `top` largest one after the other.
+constexpr int ROUTE_WARPS = 8;
+
+template <typename T>
+__device__ __forceinline__ float route_dot(const T* __restrict__ row, const float* __restrict__ wr, int width, int lane,
+                                           bool vec) {
+    float dot = 0.f;
+    if (vec) {
+        for (int c = lane * 4; c < width; c += 128) {
+            const float4 wv = *reinterpret_cast<const float4*>(wr + c);
+            dot = fmaf(to_float(row[c]), wv.x, dot);
+            dot = fmaf(to_float(row[c + 1]), wv.y, dot);
+            dot = fmaf(to_float(row[c + 2]), wv.z, dot);
+            dot = fmaf(to_float(row[c + 3]), wv.w, dot);
+        }
+    } else {
+        for (int c = lane; c < width; c += 32) dot = fmaf(to_float(row[c]), wr[c], dot);
+    }
+    return warp_sum(dot);
+}
 
 template <typename T>
 __global__ void __launch_bounds__(32 * ROUTE_WARPS)
 moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w_router, const float* __restrict__ w_gate,
                  const int* __restrict__ positions, int* __restrict__ ids, float* __restrict__ weights,
                  float* __restrict__ gate, int n_tokens, int width, int n_experts, int top) {
-    extern __shared__ float z_smem[];                      // [ROUTE_WARPS][n_experts]
+    extern __shared__ float z[];                           // [n_experts]
     pdl_trigger();
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int token = blockIdx.x * ROUTE_WARPS + warp;
-    if (token >= n_tokens) return;
+    const int token = blockIdx.x;
     if (positions != nullptr && positions[token] < 0) {    // padding of a fixed-size batch: no expert
-        for (int k = lane; k < top; k += 32) {
+        for (int k = threadIdx.x; k < top; k += blockDim.x) {
             ids[(size_t)token * top + k] = -1;
             weights[(size_t)token * top + k] = 0.f;
         }
-        if (gate != nullptr && lane == 0) gate[token] = 0.f;
+        if (gate != nullptr && threadIdx.x == 0) gate[token] = 0.f;
         return;
     }
-    float* z = z_smem + warp * n_experts;
     const T* row = h + (size_t)token * width;
-    for (int e = 0; e < n_experts; ++e) {
-        const float* wr = w_router + (size_t)e * width;
-        float dot = 0.f;
-        for (int c = lane; c < width; c += 32) dot = fmaf(to_float(row[c]), wr[c], dot);
-        dot = warp_sum(dot);
-        if (lane == 0) z[e] = dot;
+    const bool vec = width % 4 == 0 && ((uintptr_t)w_router % 16 == 0) && (w_gate == nullptr || (uintptr_t)w_gate % 16 == 0);
+    const int rows = n_experts + (gate != nullptr ? 1 : 0);
+    for (int e = warp; e < rows; e += ROUTE_WARPS) {
+        const float dot = route_dot(row, e < n_experts ? w_router + (size_t)e * width : w_gate, width, lane, vec);
+        if (lane == 0) {
+            if (e < n_experts) z[e] = dot;
+            else gate[token] = 1.0f / (1.0f + expf(-dot));
+        }
     }
-    if (gate != nullptr) {
-        float dot = 0.f;
-        for (int c = lane; c < width; c += 32) dot = fmaf(to_float(row[c]), w_gate[c], dot);
-        dot = warp_sum(dot);
-        if (lane == 0) gate[token] = 1.0f / (1.0f + expf(-dot));
-    }
-    __syncwarp();
+    __syncthreads();
+    if (warp != 0) return;
     // the `top` largest, one after the other; every lane looks at a share of the experts
     float z_max = 0.f, sum = 0.f;
     for (int k = 0; k < top; ++k) {
@@ -72,6 +88,7 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w_router, co
             const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
             if (ov > best || (ov == best && oe < best_e)) best = ov, best_e = oe;
         }
+        if (best_e >= n_experts) best_e = k;               // logits that are not numbers: still a valid choice
         if (k == 0) z_max = best;
         const float p = expf(best - z_max);
         sum += p;
@@ -238,6 +255,158 @@ moe_gemm_kernel(const T* __restrict__ x, int ldx, const T* __restrict__ w, long 
     }
 }
 
+// ---- the same products on the warp-level tensor cores (bfloat16, K a multiple of 8) -------------------
+// Tiles of 64 slots x 128 rows of the expert's matrix, 32 of K at a time through two shared-memory
+// buffers (the next tile's global loads are in flight while this one is multiplied); four warps as
+// 2 x 2, each 32 slots x 64 matrix rows.  For the gated product a warp's 64 rows are 32 gate rows and
+// the 32 up rows of the same outputs, so silu(gate) * up happens in the accumulators.
+constexpr int MT = 64, MB = 128, MK = 32, MLD = MK + 8;
+
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix4(uint32_t (&r)[4], const bf16* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+
+template <bool GLU>
+__global__ void __launch_bounds__(128)
+moe_gemm_mma_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ w, long long w_expert_stride,
+                    const int* __restrict__ offsets, const int* __restrict__ slot_entry, int top,
+                    const float* __restrict__ scale, void* __restrict__ out, int N, int K, int x_rows) {
+    __shared__ __align__(16) bf16 as[2][MT * MLD];
+    __shared__ __align__(16) bf16 bs[2][MB * MLD];
+    __shared__ int row_of[MT];
+    pdl_trigger();
+    pdl_wait();
+    const int e = blockIdx.z;
+    const int first = offsets[e], count = offsets[e + 1] - first;
+    const int m0 = blockIdx.y * MT;
+    if (m0 >= count) return;
+    const int n0 = blockIdx.x * (GLU ? 64 : 128);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid < MT) {
+        int r = -1;
+        if (m0 + tid < count) {
+            const int slot = first + m0 + tid;
+            r = GLU ? slot_entry[slot] / top : slot;
+            if (!MG_GUARDED(moe, MG_GUARD_ROW, r, x_rows)) r = -1;
+        }
+        row_of[tid] = r;
+    }
+    __syncthreads();
+    const bf16* we = w + (size_t)e * w_expert_stride;
+    // what this thread copies per tile: 2 chunks of 8 activations, 4 chunks of 8 weights
+    const bf16* a_src[2];
+    const bf16* b_src[4];
+    int a_dst[2], b_dst[4];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const int i = tid + 128 * u, row = i >> 2, c = i & 3;
+        a_src[u] = row_of[row] >= 0 ? x + (size_t)row_of[row] * ldx + c * 8 : nullptr;
+        a_dst[u] = row * MLD + c * 8;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int i = tid + 128 * u, row = i >> 2, c = i & 3;
+        int n, wrow;
+        if (GLU) {
+            const int r = row & 63;
+            n = n0 + (row >> 6) * 32 + (r & 31);
+            wrow = r < 32 ? n : N + n;
+        } else {
+            n = n0 + row;
+            wrow = n;
+        }
+        b_src[u] = n < N ? we + (size_t)wrow * K + c * 8 : nullptr;
+        b_dst[u] = row * MLD + c * 8;
+    }
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    uint4 a_reg[2], b_reg[4];
+    auto fetch = [&](int k0) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+            a_reg[u] = (a_src[u] && k0 + (int)((tid + 128 * u) & 3) * 8 < K) ? *reinterpret_cast<const uint4*>(a_src[u] + k0) : zero;
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            b_reg[u] = (b_src[u] && k0 + (int)((tid + 128 * u) & 3) * 8 < K) ? *reinterpret_cast<const uint4*>(b_src[u] + k0) : zero;
+    };
+    auto stash = [&](int buf) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u) *reinterpret_cast<uint4*>(&as[buf][a_dst[u]]) = a_reg[u];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) *reinterpret_cast<uint4*>(&bs[buf][b_dst[u]]) = b_reg[u];
+    };
+    const int wr = warp >> 1, wc = warp & 1;
+    float acc[2][8][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
+    const int iters = (K + MK - 1) / MK;
+    fetch(0);
+    stash(0);
+    __syncthreads();
+    for (int it = 0; it < iters; ++it) {
+        const int buf = it & 1;
+        if (it + 1 < iters) fetch((it + 1) * MK);
+#pragma unroll
+        for (int kk = 0; kk < MK / 16; ++kk) {
+            uint32_t af[2][4];
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+                ldmatrix4(af[i], &as[buf][(wr * 32 + i * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * MLD + kk * 16 + (lane >> 4) * 8]);
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) {
+                uint32_t bf[4];
+                ldmatrix4(bf, &bs[buf][(wc * 64 + j * 8 + (lane >> 4) * 8 + (lane & 7)) * MLD + kk * 16 + ((lane >> 3) & 1) * 8]);
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    mma_16816(acc[i][j], af[i], bf[0], bf[1]);
+                    mma_16816(acc[i][j + 1], af[i], bf[2], bf[3]);
+                }
+            }
+        }
+        if (it + 1 < iters) stash(buf ^ 1);
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int m = m0 + wr * 32 + i * 16 + (lane >> 2) + 8 * half;
+            if (m >= count) continue;
+            const size_t slot = (size_t)first + m;
+            if (GLU) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int n = n0 + wc * 32 + j * 8 + 2 * (lane & 3);
+                    const float v0 = silu(acc[i][j][2 * half]) * acc[i][j + 4][2 * half];
+                    const float v1 = silu(acc[i][j][2 * half + 1]) * acc[i][j + 4][2 * half + 1];
+                    bf16* o = reinterpret_cast<bf16*>(out) + slot * N + n;
+                    if (n + 1 < N && (N & 1) == 0) *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(v0, v1);
+                    else {
+                        if (n < N) o[0] = __float2bfloat16_rn(v0);
+                        if (n + 1 < N) o[1] = __float2bfloat16_rn(v1);
+                    }
+                }
+            } else {
+                const float sc = scale[slot_entry[slot]];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int n = n0 + wc * 64 + j * 8 + 2 * (lane & 3);
+                    float* o = reinterpret_cast<float*>(out) + slot * N + n;
+                    if (n < N) o[0] = acc[i][j][2 * half] * sc;
+                    if (n + 1 < N) o[1] = acc[i][j][2 * half + 1] * sc;
+                }
+            }
+        }
+}
+
 // ---- x[token] += sum over the token's entries, in entry order ----------------------------------
 __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ entry_slot, int top,
                                    float* __restrict__ residual, int width, int n_slots) {
@@ -269,6 +438,8 @@ __global__ void glu_kernel(const T* __restrict__ gu, const float* __restrict__ s
     out[i] = from_float<T>(v);
 }
 
+inline dim3 block128() { return dim3(128); }
+
 #define MG_LAUNCHED(e, name)                                                                 \
     do {                                                                                     \
         if ((e) != cudaSuccess) return mg_set_error(MG_ERR_CUDA, name ": %s", cudaGetErrorString(e)); \
@@ -285,9 +456,9 @@ MG_API int mg_moe_route(const void* h, const float* w_router, const float* w_gat
     if (n_tokens == 0) return MG_OK;
     MG_REQUIRE(n_tokens > 0 && width > 0 && n_experts > 0 && top > 0 && top <= n_experts, "moe route: bad sizes");
     MG_REQUIRE((w_gate == nullptr) == (gate == nullptr), "moe route: a gate wants its weights and its output");
-    const size_t smem = (size_t)ROUTE_WARPS * n_experts * sizeof(float);
+    const size_t smem = (size_t)n_experts * sizeof(float);
     MG_REQUIRE(smem <= 48 * 1024, "moe route: too many experts (%d)", n_experts);
-    const dim3 grid(ceil_div(n_tokens, ROUTE_WARPS)), block(32 * ROUTE_WARPS);
+    const dim3 grid(n_tokens), block(32 * ROUTE_WARPS);
     cudaError_t e;
     if (is_bf16)
         e = mg_launch(moe_route_kernel<bf16>, grid, block, smem, (cudaStream_t)stream, true, (const bf16*)h, w_router,
@@ -325,7 +496,17 @@ MG_API int mg_moe_gemm(const void* x, int ldx, const void* w, const int* offsets
     const long long stride = (long long)(glu ? 2 : 1) * N * K;
     cudaStream_t s = (cudaStream_t)stream;
     cudaError_t e;
-    if (is_bf16 && glu)
+    const bool tensor_cores = is_bf16 && K % 8 == 0 && ldx % 8 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 &&
+                              (uintptr_t)out % 4 == 0;
+    if (tensor_cores) {
+        const dim3 tgrid(ceil_div(N, glu ? 64 : 128), ceil_div(max_rows, MT), n_experts);
+        if (glu)
+            e = mg_launch(moe_gemm_mma_kernel<true>, tgrid, block128(), 0, s, true, (const bf16*)x, ldx, (const bf16*)w, stride,
+                          offsets, slot_entry, top, scale, out, N, K, x_rows);
+        else
+            e = mg_launch(moe_gemm_mma_kernel<false>, tgrid, block128(), 0, s, true, (const bf16*)x, ldx, (const bf16*)w,
+                          stride, offsets, slot_entry, top, scale, out, N, K, x_rows);
+    } else if (is_bf16 && glu)
         e = mg_launch(moe_gemm_kernel<bf16, true>, grid, block, 0, s, true, (const bf16*)x, ldx, (const bf16*)w, stride,
                       offsets, slot_entry, top, scale, out, N, K, x_rows);
     else if (is_bf16)
