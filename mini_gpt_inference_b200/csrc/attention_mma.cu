@@ -131,8 +131,8 @@ __device__ __forceinline__ void load_q(uint32_t (&qf)[DP / 16][4], const bf16* q
 // visible key (pos < 0: a row without a token).
 template <int DP, int DVP, int NT>
 __device__ __forceinline__ void attend(const uint32_t (&qf)[DP / 16][4], const bf16* ks, const bf16* vs, int k_first,
-                                       int j_first, const int (&pos)[2], const int (&lo)[2], float scale_log2,
-                                       float (&m)[2], float (&l)[2], float (&o)[DVP / 8][4], int lane) {
+                                       int j_first, const int (&pos)[2], const int (&lo)[2], bool all_visible,
+                                       float scale_log2, float (&m)[2], float (&l)[2], float (&o)[DVP / 8][4], int lane) {
     float s[NT][4];
 #pragma unroll
     for (int n = 0; n < NT; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
@@ -146,24 +146,35 @@ __device__ __forceinline__ void attend(const uint32_t (&qf)[DP / 16][4], const b
             mma16816(s[n + 1], qf[kk], b[2], b[3]);
         }
     }
-    // masks and the block's maximum per row
+    // masks and the block's maximum per row (all_visible, the same for the whole warp: every row of
+    // the warp sees every key of these, nothing to compare)
     float bm[2] = {-INFINITY, -INFINITY};
+    if (all_visible) {
 #pragma unroll
-    for (int n = 0; n < NT; ++n)
+        for (int n = 0; n < NT; ++n)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int j = j_first + n * 8 + 2 * (lane & 3) + (e & 1), r = e >> 1;
-            const float v = (j <= pos[r] && j >= lo[r]) ? s[n][e] * scale_log2 : -INFINITY;
-            s[n][e] = v;
-            bm[r] = fmaxf(bm[r], v);
-        }
+            for (int e = 0; e < 4; ++e) {
+                s[n][e] *= scale_log2;
+                bm[e >> 1] = fmaxf(bm[e >> 1], s[n][e]);
+            }
+    } else {
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int j = j_first + n * 8 + 2 * (lane & 3) + (e & 1), r = e >> 1;
+                const float v = (j <= pos[r] && j >= lo[r]) ? s[n][e] * scale_log2 : -INFINITY;
+                s[n][e] = v;
+                bm[r] = fmaxf(bm[r], v);
+            }
+    }
     float corr[2], base[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         bm[r] = fmaxf(bm[r], __shfl_xor_sync(0xffffffffu, bm[r], 1));
         bm[r] = fmaxf(bm[r], __shfl_xor_sync(0xffffffffu, bm[r], 2));
         const float nm = fmaxf(m[r], bm[r]);
-        corr[r] = (m[r] == -INFINITY) ? 0.f : exp2f(m[r] - nm);
+        corr[r] = (m[r] == -INFINITY) ? 0.f : exp2_approx(m[r] - nm);
         base[r] = (nm == -INFINITY) ? 0.f : nm;            // a row that has seen no key yet: weights stay 0
         m[r] = nm;
     }
@@ -172,7 +183,7 @@ __device__ __forceinline__ void attend(const uint32_t (&qf)[DP / 16][4], const b
     for (int n = 0; n < NT; ++n)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            const float pr = exp2f(s[n][e] - base[e >> 1]);
+            const float pr = exp2_approx(s[n][e] - base[e >> 1]);
             s[n][e] = pr;
             bs[e >> 1] += pr;
         }
@@ -261,6 +272,9 @@ attention_tiles_kernel(const AttnParams p) {
     // the last key this warp's rows can see (rows are in token order)
     const int warp_last_token = min(count - 1, (warp * 16 + 15) / group);
     const int warp_hi = (warp * 16) / group < count ? p.positions[first + warp_last_token] : -1;
+    // blocks that all rows of the warp see whole: up to the warp's first token, from the last one's window on
+    const int warp_first_pos = (warp * 16) / group < count ? p.positions[first + (warp * 16) / group] : -1;
+    const int warp_max_lo = (p.window > 0 && warp_hi >= 0) ? max(0, warp_hi - p.window + 1) : 0;
 
     // two buffers take turns: the next block's copies are in flight while this one is multiplied
     const int j_begin = (lo_tile / KB) * KB;
@@ -277,7 +291,8 @@ attention_tiles_kernel(const AttnParams p) {
         }
         __syncthreads();
         if (j0 <= warp_hi)
-            attend<DP, DVP, 8>(qf, ks + buf * STAGE, vs + buf * STAGE, 0, j0, pos, lo, p.scale_log2, m, l, o, lane);
+            attend<DP, DVP, 8>(qf, ks + buf * STAGE, vs + buf * STAGE, 0, j0, pos, lo,
+                               j0 + KB - 1 <= warp_first_pos && j0 >= warp_max_lo, p.scale_log2, m, l, o, lane);
         __syncthreads();                                    // the buffer is free for the block after the next
     }
 #pragma unroll
@@ -355,8 +370,8 @@ attention_split_kernel(const AttnParams p) {
             }
             __syncthreads();
             if (j0 + warp * 16 <= last)
-                attend<DP, DVP, 2>(qf, ks + buf * STAGE, vs + buf * STAGE, warp * 16, j0 + warp * 16, pos, lo, p.scale_log2, m, l,
-                                   o, lane);
+                attend<DP, DVP, 2>(qf, ks + buf * STAGE, vs + buf * STAGE, warp * 16, j0 + warp * 16, pos, lo, false,
+                                   p.scale_log2, m, l, o, lane);
             __syncthreads();
         }
     }

@@ -55,6 +55,7 @@ struct MlpArgs {
     const bf16* w2p;                 // proj.weight packed for this kernel, see mg_mlp_pack_elements()
     const float* b2;                 // [C] or null
     int M, C, F;
+    int activation;                  // 0: tanh-GELU, 1: the square of the positive part
 };
 
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
@@ -267,8 +268,10 @@ __global__ void __launch_bounds__(THREADS, 1) mlp_fused_kernel(const MlpArgs a) 
                 v1 += p.y;
             }
             // units past the inner width (a ragged last CTA) count as zero
-            v0 = (m < a.M && f0 + unit < F) ? gelu_tanh(v0 + bias1[0]) : 0.f;
-            v1 = (m < a.M && f0 + unit + 1 < F) ? gelu_tanh(v1 + bias1[1]) : 0.f;
+            v0 += bias1[0];
+            v1 += bias1[1];
+            v0 = (m < a.M && f0 + unit < F) ? (a.activation == 1 ? relu_sq(v0) : gelu_tanh(v0)) : 0.f;
+            v1 = (m < a.M && f0 + unit + 1 < F) ? (a.activation == 1 ? relu_sq(v1) : gelu_tanh(v1)) : 0.f;
             *reinterpret_cast<uint32_t*>(hs + m * HSTRIDE + unit) = pack2(v0, v1);
         }
     }
@@ -355,17 +358,19 @@ MG_API int mg_mlp_fused_max_width() { return MAX_WIDTH; }
 // that copy once per matrix; this is its length in elements.
 MG_API long long mg_mlp_pack_elements(int C, int F) { return (long long)((F + FS - 1) / FS) * FS * C; }
 
-// out = x + proj(gelu_tanh(fc(LayerNorm(x)) + b1)) + b2 for M <= 16 tokens, bfloat16 weights.
+// out = x + proj(act(fc(LayerNorm(x)) + b1)) + b2 for M <= 16 tokens, bfloat16 weights; act is
+// tanh-GELU (activation 0) or the square of the positive part (1).
 // w2_packed: proj.weight in the order of mg_mlp_pack_elements().  x, out, spare: three different
 // [M, C] 32-bit buffers; out must be all zeros on entry; spare is all zeros on exit.  Returns MG_ERR_UNSUPPORTED for sizes it does not take (the caller then runs
 // the two projections).
 MG_API int mg_mlp_fused(const float* x, float* out, float* spare, const float* gain, const float* shift, float eps,
                         const void* w1, const float* b1, const void* w2_packed, const float* b2, int M, int C, int F,
-                        void* stream) {
+                        int activation, void* stream) {
     if (M == 0) return MG_OK;
     MG_REQUIRE(M > 0 && C > 0 && F > 0, "feed-forward: bad sizes M=%d C=%d F=%d", M, C, F);
     MG_REQUIRE(x && out && spare && gain && w1 && w2_packed, "feed-forward: missing operand");
     MG_REQUIRE(x != out && x != spare && out != spare, "feed-forward: x, out and spare must be three buffers");
+    MG_REQUIRE(activation == 0 || activation == 1, "feed-forward: unknown activation %d", activation);
     const int mt = M <= 8 ? 8 : 16;
     const size_t smem = mlp_smem(mt, C);
     if (M > 16 || C > MAX_WIDTH || C % 8 != 0 || F % 8 != 0 || smem > 200 * 1024 || ((uintptr_t)w1 & 15) || ((uintptr_t)w2_packed & 15) ||
@@ -374,7 +379,7 @@ MG_API int mg_mlp_fused(const float* x, float* out, float* spare, const float* g
         return mg_set_error(MG_ERR_UNSUPPORTED, "feed-forward (fused): needs M <= 16, width <= 512, widths that are multiples of 8, aligned operands");
     MlpArgs a;
     a.x = x; a.out = out; a.spare = spare; a.gain = gain; a.shift = shift; a.eps = eps;
-    a.w1 = (const bf16*)w1; a.b1 = b1; a.w2p = (const bf16*)w2_packed; a.b2 = b2; a.M = M; a.C = C; a.F = F;
+    a.w1 = (const bf16*)w1; a.b1 = b1; a.w2p = (const bf16*)w2_packed; a.b2 = b2; a.M = M; a.C = C; a.F = F; a.activation = activation;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaSuccess;

@@ -256,11 +256,12 @@ moe_gemm_kernel(const T* __restrict__ x, int ldx, const T* __restrict__ w, long 
 }
 
 // ---- the same products on the warp-level tensor cores (bfloat16, K a multiple of 8) -------------------
-// Tiles of 64 slots x 128 rows of the expert's matrix, 32 of K at a time through two shared-memory
-// buffers (the next tile's global loads are in flight while this one is multiplied); four warps as
+// Tiles of 64 slots x 128 rows of the expert's matrix, 64 of K at a time through two shared-memory
+// buffers (cp.async: the next tile's copies are in flight while this one is multiplied); four warps as
 // 2 x 2, each 32 slots x 64 matrix rows.  For the gated product a warp's 64 rows are 32 gate rows and
 // the 32 up rows of the same outputs, so silu(gate) * up happens in the accumulators.
-constexpr int MT = 64, MB = 128, MK = 32, MLD = MK + 8;
+constexpr int MT = 64, MB = 128, MK = 64, MLD = MK + 8;
+constexpr size_t MOE_MMA_SMEM = (size_t)2 * (MT + MB) * MLD * sizeof(bf16);
 
 __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -272,14 +273,21 @@ __device__ __forceinline__ void ldmatrix4(uint32_t (&r)[4], const bf16* p) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
 }
+// 16 bytes from global to shared memory, asynchronously; `real` false: zeros, nothing is read.
+__device__ __forceinline__ void copy16_async(bf16* dst, const bf16* src, bool real) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    const int bytes = real ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
 
 template <bool GLU>
 __global__ void __launch_bounds__(128)
 moe_gemm_mma_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ w, long long w_expert_stride,
                     const int* __restrict__ offsets, const int* __restrict__ slot_entry, int top,
                     const float* __restrict__ scale, void* __restrict__ out, int N, int K, int x_rows) {
-    __shared__ __align__(16) bf16 as[2][MT * MLD];
-    __shared__ __align__(16) bf16 bs[2][MB * MLD];
+    extern __shared__ __align__(16) uint8_t moe_smem[];
+    bf16* as = reinterpret_cast<bf16*>(moe_smem);          // [2][MT * MLD]
+    bf16* bs = as + 2 * MT * MLD;                          // [2][MB * MLD]
     __shared__ int row_of[MT];
     pdl_trigger();
     pdl_wait();
@@ -300,19 +308,18 @@ moe_gemm_mma_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
     }
     __syncthreads();
     const bf16* we = w + (size_t)e * w_expert_stride;
-    // what this thread copies per tile: 2 chunks of 8 activations, 4 chunks of 8 weights
-    const bf16* a_src[2];
-    const bf16* b_src[4];
-    int a_dst[2], b_dst[4];
-#pragma unroll
-    for (int u = 0; u < 2; ++u) {
-        const int i = tid + 128 * u, row = i >> 2, c = i & 3;
-        a_src[u] = row_of[row] >= 0 ? x + (size_t)row_of[row] * ldx + c * 8 : nullptr;
-        a_dst[u] = row * MLD + c * 8;
-    }
+    // what this thread copies per tile: 4 chunks of 8 activations, 8 chunks of 8 weights
+    const bf16* a_src[4];
+    const bf16* b_src[8];
+    const int chunk = (tid & 7) * 8;                       // the same column for all of a thread's chunks
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-        const int i = tid + 128 * u, row = i >> 2, c = i & 3;
+        const int row = (tid + 128 * u) >> 3;
+        a_src[u] = row_of[row] >= 0 ? x + (size_t)row_of[row] * ldx + chunk : nullptr;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        const int row = (tid + 128 * u) >> 3;
         int n, wrow;
         if (GLU) {
             const int r = row & 63;
@@ -322,24 +329,21 @@ moe_gemm_mma_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
             n = n0 + row;
             wrow = n;
         }
-        b_src[u] = n < N ? we + (size_t)wrow * K + c * 8 : nullptr;
-        b_dst[u] = row * MLD + c * 8;
+        b_src[u] = n < N ? we + (size_t)wrow * K + chunk : nullptr;
     }
-    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-    uint4 a_reg[2], b_reg[4];
-    auto fetch = [&](int k0) {
+    auto issue = [&](int buf, int k0) {
+        const bool in_k = k0 + chunk < K;
 #pragma unroll
-        for (int u = 0; u < 2; ++u)
-            a_reg[u] = (a_src[u] && k0 + (int)((tid + 128 * u) & 3) * 8 < K) ? *reinterpret_cast<const uint4*>(a_src[u] + k0) : zero;
+        for (int u = 0; u < 4; ++u) {
+            const bool real = a_src[u] != nullptr && in_k;
+            copy16_async(as + buf * MT * MLD + ((tid + 128 * u) >> 3) * MLD + chunk, real ? a_src[u] + k0 : x, real);
+        }
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
-            b_reg[u] = (b_src[u] && k0 + (int)((tid + 128 * u) & 3) * 8 < K) ? *reinterpret_cast<const uint4*>(b_src[u] + k0) : zero;
-    };
-    auto stash = [&](int buf) {
-#pragma unroll
-        for (int u = 0; u < 2; ++u) *reinterpret_cast<uint4*>(&as[buf][a_dst[u]]) = a_reg[u];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) *reinterpret_cast<uint4*>(&bs[buf][b_dst[u]]) = b_reg[u];
+        for (int u = 0; u < 8; ++u) {
+            const bool real = b_src[u] != nullptr && in_k;
+            copy16_async(bs + buf * MB * MLD + ((tid + 128 * u) >> 3) * MLD + chunk, real ? b_src[u] + k0 : w, real);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
     };
     const int wr = warp >> 1, wc = warp & 1;
     float acc[2][8][4];
@@ -348,22 +352,28 @@ moe_gemm_mma_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
     const int iters = (K + MK - 1) / MK;
-    fetch(0);
-    stash(0);
-    __syncthreads();
+    issue(0, 0);
     for (int it = 0; it < iters; ++it) {
         const int buf = it & 1;
-        if (it + 1 < iters) fetch((it + 1) * MK);
+        if (it + 1 < iters) {
+            issue(buf ^ 1, (it + 1) * MK);                  // in flight while this tile is multiplied
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        const bf16* at = as + buf * MT * MLD;
+        const bf16* bt = bs + buf * MB * MLD;
 #pragma unroll
         for (int kk = 0; kk < MK / 16; ++kk) {
             uint32_t af[2][4];
 #pragma unroll
             for (int i = 0; i < 2; ++i)
-                ldmatrix4(af[i], &as[buf][(wr * 32 + i * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * MLD + kk * 16 + (lane >> 4) * 8]);
+                ldmatrix4(af[i], at + (wr * 32 + i * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * MLD + kk * 16 + (lane >> 4) * 8);
 #pragma unroll
             for (int j = 0; j < 8; j += 2) {
                 uint32_t bf[4];
-                ldmatrix4(bf, &bs[buf][(wc * 64 + j * 8 + (lane >> 4) * 8 + (lane & 7)) * MLD + kk * 16 + ((lane >> 3) & 1) * 8]);
+                ldmatrix4(bf, bt + (wc * 64 + j * 8 + (lane >> 4) * 8 + (lane & 7)) * MLD + kk * 16 + ((lane >> 3) & 1) * 8);
 #pragma unroll
                 for (int i = 0; i < 2; ++i) {
                     mma_16816(acc[i][j], af[i], bf[0], bf[1]);
@@ -371,8 +381,7 @@ moe_gemm_mma_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
                 }
             }
         }
-        if (it + 1 < iters) stash(buf ^ 1);
-        __syncthreads();
+        __syncthreads();                                    // the buffer is free for the tile after the next
     }
 #pragma unroll
     for (int i = 0; i < 2; ++i)
@@ -500,11 +509,19 @@ MG_API int mg_moe_gemm(const void* x, int ldx, const void* w, const int* offsets
                               (uintptr_t)out % 4 == 0;
     if (tensor_cores) {
         const dim3 tgrid(ceil_div(N, glu ? 64 : 128), ceil_div(max_rows, MT), n_experts);
+        static bool configured = false;
+        if (!configured) {
+            e = cudaFuncSetAttribute(moe_gemm_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MOE_MMA_SMEM);
+            if (e == cudaSuccess)
+                e = cudaFuncSetAttribute(moe_gemm_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MOE_MMA_SMEM);
+            MG_LAUNCHED(e, "moe gemm (shared memory)");
+            configured = true;
+        }
         if (glu)
-            e = mg_launch(moe_gemm_mma_kernel<true>, tgrid, block128(), 0, s, true, (const bf16*)x, ldx, (const bf16*)w, stride,
+            e = mg_launch(moe_gemm_mma_kernel<true>, tgrid, block128(), MOE_MMA_SMEM, s, true, (const bf16*)x, ldx, (const bf16*)w, stride,
                           offsets, slot_entry, top, scale, out, N, K, x_rows);
         else
-            e = mg_launch(moe_gemm_mma_kernel<false>, tgrid, block128(), 0, s, true, (const bf16*)x, ldx, (const bf16*)w,
+            e = mg_launch(moe_gemm_mma_kernel<false>, tgrid, block128(), MOE_MMA_SMEM, s, true, (const bf16*)x, ldx, (const bf16*)w,
                           stride, offsets, slot_entry, top, scale, out, N, K, x_rows);
     } else if (is_bf16 && glu)
         e = mg_launch(moe_gemm_kernel<bf16, true>, grid, block, 0, s, true, (const bf16*)x, ldx, (const bf16*)w, stride,

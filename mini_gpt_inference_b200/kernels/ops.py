@@ -501,7 +501,7 @@ class CudaOps:
         deferred = y if isinstance(y, DeferredNorm) else None
         m = residual32.shape[0]
         if (self.use_fused_mlp and deferred is not None and deferred.rows is None and deferred.x32 is residual32
-                and activation == "gelu_tanh" and fc_weight.dtype == torch.bfloat16 and act_dtype == torch.bfloat16
+                and activation in ("gelu_tanh", "relu_sq") and fc_weight.dtype == torch.bfloat16 and act_dtype == torch.bfloat16
                 and deferred.dtype == torch.bfloat16 and 0 < m <= self.FUSED_MLP_ROWS
                 and residual32.shape[1] <= self.lib.mg_mlp_fused_max_width() and residual32.shape[1] % 8 == 0
                 and fc_weight.shape[0] % 8 == 0):
@@ -518,7 +518,7 @@ class CudaOps:
             code = self.lib.mg_mlp_fused(_ptr(residual32), _ptr(nxt), _ptr(spare), _ptr(deferred.gain),
                                          _ptr(deferred.shift), deferred.eps, _ptr(fc_weight), _ptr(fc_bias),
                                          _ptr(self._packed_proj(proj_weight)), _ptr(proj_bias), m, c, f,
-                                         self._stream())
+                                         1 if activation == "relu_sq" else 0, self._stream())
             if code != library.UNSUPPORTED:
                 self._run(code, "feed-forward (fused)")
                 self._ring = (nxt, spare, residual32)          # nxt holds the stream; spare is zero

@@ -182,7 +182,7 @@ def test_a_kernel_that_gave_up_stops_generation(overlap):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_batch_of_seven_with_portions_of_13_and_forced_preemption(dtype):
-    """The second tiny configuration as the task's list words it (MLP 384, eps 1e-5, pages of 8):
+    """The third tiny configuration (MLP 384, eps 1e-5, pages of 8):
     prompts of 1 to 100 tokens, seven running at a time, prompt portions of at most 13 tokens, and a
     pool too small for seven long requests, so that some give way and are recomputed."""
     cfg, tensors, engine = engine_for("C", dtype, sharp=False, block_size=8, num_blocks=44, max_batch_size=7,
