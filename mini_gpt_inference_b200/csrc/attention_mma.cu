@@ -83,19 +83,26 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+// A warp copies 16 of the block's 64 rows; a row's 16-byte chunks (keys first, then values) go to
+// neighbouring lanes, 8, 16 or 32 lanes per row, so no division sits in the loop (page sizes that
+// are powers of two index their pages by shifts: page_shift >= 0).
 template <int DP, int DVP>
 __device__ __forceinline__ void load_block(const AttnParams& p, const int* table, int kv_head, int j0, int lo, int hi,
-                                           bf16* ks, bf16* vs, int tid, int threads) {
-    const int kc = p.d / 8, vc = p.dv / 8;               // 16-byte chunks per row
-    for (int i = tid; i < KB * (kc + vc); i += threads) {
-        const int key = i / (kc + vc), c = i - key * (kc + vc);
+                                           bf16* ks, bf16* vs, int warp, int lane, int page_shift) {
+    const int kc = p.d >> 3, chunks = kc + (p.dv >> 3);  // 16-byte chunks per row, at most 32
+    const int lane_shift = chunks <= 8 ? 3 : chunks <= 16 ? 4 : 5;
+    const int c = lane & ((1 << lane_shift) - 1);
+    for (int key = warp * 16 + (lane >> lane_shift); key < warp * 16 + 16; key += 32 >> lane_shift) {
+        if (c >= chunks) continue;
         const int j = j0 + key;
         const bool real = j >= lo && j <= hi;
         size_t row = 0;
         if (real) {
-            int page = table[j / p.page_tokens];
+            const int index = page_shift >= 0 ? j >> page_shift : j / p.page_tokens;
+            const int within = page_shift >= 0 ? j & (p.page_tokens - 1) : j - index * p.page_tokens;
+            int page = table[index];
             if (!MG_GUARDED(attention_mma, MG_GUARD_PAGE, page, p.num_pages)) page = 0;
-            row = ((size_t)page * p.n_kv_head + kv_head) * p.page_tokens + (j % p.page_tokens);
+            row = ((size_t)page * p.n_kv_head + kv_head) * p.page_tokens + within;
         }
         if (c < kc) cp_async16(ks + key * (DP + PAD) + c * 8, p.k_pages + row * p.d + c * 8, real);
         else cp_async16(vs + key * (DVP + PAD) + (c - kc) * 8, p.v_pages + row * p.dv + (c - kc) * 8, real);
@@ -278,12 +285,14 @@ attention_tiles_kernel(const AttnParams p) {
 
     // two buffers take turns: the next block's copies are in flight while this one is multiplied
     const int j_begin = (lo_tile / KB) * KB;
-    load_block<DP, DVP>(p, table, kv_head, j_begin, lo_tile, hi, ks, vs, tid, 128);
+    const int page_shift = (p.page_tokens & (p.page_tokens - 1)) == 0 ? __ffs(p.page_tokens) - 1 : -1;
+    load_block<DP, DVP>(p, table, kv_head, j_begin, lo_tile, hi, ks, vs, warp, lane, page_shift);
     cp_async_commit();
     int buf = 0;
     for (int j0 = j_begin; j0 <= hi; j0 += KB, buf ^= 1) {
         if (j0 + KB <= hi) {
-            load_block<DP, DVP>(p, table, kv_head, j0 + KB, lo_tile, hi, ks + (buf ^ 1) * STAGE, vs + (buf ^ 1) * STAGE, tid, 128);
+            load_block<DP, DVP>(p, table, kv_head, j0 + KB, lo_tile, hi, ks + (buf ^ 1) * STAGE, vs + (buf ^ 1) * STAGE, warp, lane,
+                                page_shift);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
@@ -357,12 +366,14 @@ attention_split_kernel(const AttnParams p) {
         }
         uint32_t qf[DP / 16][4];
         load_q<DP>(qf, qrow[0], qrow[1], p.d, lane);
-        load_block<DP, DVP>(p, table, kv_head, first, lo_row, last, ks, vs, tid, 128);
+        const int page_shift = (p.page_tokens & (p.page_tokens - 1)) == 0 ? __ffs(p.page_tokens) - 1 : -1;
+        load_block<DP, DVP>(p, table, kv_head, first, lo_row, last, ks, vs, warp, lane, page_shift);
         cp_async_commit();
         int buf = 0;
         for (int j0 = first; j0 <= last; j0 += KB, buf ^= 1) {
             if (j0 + KB <= last) {
-                load_block<DP, DVP>(p, table, kv_head, j0 + KB, lo_row, last, ks + (buf ^ 1) * STAGE, vs + (buf ^ 1) * STAGE, tid, 128);
+                load_block<DP, DVP>(p, table, kv_head, j0 + KB, lo_row, last, ks + (buf ^ 1) * STAGE, vs + (buf ^ 1) * STAGE, warp,
+                                    lane, page_shift);
                 cp_async_commit();
                 cp_async_wait<1>();
             } else {
