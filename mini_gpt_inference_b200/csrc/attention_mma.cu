@@ -228,7 +228,7 @@ __device__ __forceinline__ float logistic(float x) { return 1.0f / (1.0f + expf(
 
 // ---- portions of prompts ---------------------------------------------------------------------------
 template <int DP, int DVP>
-__global__ void __launch_bounds__(128, (DP + DVP <= 128) ? 3 : ((DP + DVP <= 192) ? 2 : 1))
+__global__ void __launch_bounds__(128, (DP + DVP <= 160) ? 3 : ((DP + DVP <= 192) ? 2 : 1))
 attention_tiles_kernel(const AttnParams p) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     constexpr int STAGE = KB * (DP + PAD + DVP + PAD);     // elements of one buffer: keys, then values
