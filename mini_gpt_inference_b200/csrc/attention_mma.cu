@@ -13,8 +13,9 @@
 //          request and tile from the requests' token counts on the device.
 //   split  (single tokens): a CTA is one token, one key/value head and one range of keys; the
 //          group's heads are the rows of one m16 tile, each warp takes 16 of a block's 64 keys, the
-//          warps' partial results meet in shared memory and go to scratch; a second kernel merges
-//          the ranges, applies the gate and stores.
+//          warps' partial results meet in shared memory and go to scratch; the CTA that finishes a
+//          (token, key/value head) last merges the ranges, applies the gate and stores (or a second
+//          kernel does, if no counters are given).
 //
 // Keys are always read from the pages, whichever step wrote them.  Rows of pages beyond a request's
 // last key are never multiplied into a result (their values are replaced by zeros in shared memory).
@@ -45,6 +46,7 @@ struct AttnParams {
     bf16* out;                    // [n_tokens, H * DV]
     float* part_o;                // split: [n_tokens, H, splits, DV]
     float* part_ml;               // split: [n_tokens, H, splits, 2]
+    int* counters;                // split: [n_tokens, G] zeros, left as zeros (null: a second kernel merges)
     int n_tokens, n_requests, n_head, n_kv_head, d, dv, page_tokens, max_pages, window, num_pages;
     int tile_tokens;              // tiles: tokens per tile
     int splits, split_keys;       // split: ranges of keys per token
@@ -346,6 +348,15 @@ attention_split_kernel(const AttnParams p) {
     const int lo_row = (p.window > 0 && !padding) ? max(0, position - p.window + 1) : 0;
     const int first = (lo_row / KB) * KB + split * p.split_keys;         // ranges start at the window's block
     const int last = min(position, first + p.split_keys - 1);
+    // ranges that hold keys of this token; the others have nothing to do (the grid is sized for the
+    // longest context there can be)
+    const int live = padding ? 0 : (position - (lo_row / KB) * KB) / p.split_keys + 1;
+    if (split >= live) {
+        if (padding && split == 0)                                        // a padding row's output is zeros
+            for (int i = tid; i < group * p.dv; i += 128)
+                p.out[(size_t)token * p.n_head * p.dv + (size_t)kv_head * group * p.dv + i] = __float2bfloat16_rn(0.f);
+        return;
+    }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f}, o[DVP / 8][4];
 #pragma unroll
     for (int n = 0; n < DVP / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
@@ -359,10 +370,10 @@ attention_split_kernel(const AttnParams p) {
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             const int row = row0 + 8 * r;
-            const bool live = row < group;
-            pos[r] = live ? position : -1;
+            const bool has_row = row < group;
+            pos[r] = has_row ? position : -1;
             lo[r] = lo_row;
-            qrow[r] = live ? p.q + (size_t)token * p.q_stride + (size_t)(kv_head * group + row) * p.d : nullptr;
+            qrow[r] = has_row ? p.q + (size_t)token * p.q_stride + (size_t)(kv_head * group + row) * p.d : nullptr;
         }
         uint32_t qf[DP / 16][4];
         load_q<DP>(qf, qrow[0], qrow[1], p.d, lane);
@@ -425,6 +436,37 @@ attention_split_kernel(const AttnParams p) {
             p.part_ml[slot * 2 + 1] = sum;
         }
     }
+    if (p.counters == nullptr) return;
+    // The CTA that finishes a (token, key/value head) last merges its ranges: an arrive-only counter,
+    // nobody waits.  It leaves the counter at zero for the next launch.
+    __shared__ int is_last;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        int* counter = p.counters + (size_t)token * p.n_kv_head + kv_head;
+        is_last = atomicAdd(counter, 1) == live - 1;
+        if (is_last) *counter = 0;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int i = tid; i < group * p.dv; i += 128) {
+        const int head = kv_head * group + i / p.dv, c = i % p.dv;
+        const size_t base = ((size_t)token * p.n_head + head) * p.splits;
+        float mm = -INFINITY;
+        for (int sp = 0; sp < live; ++sp) mm = fmaxf(mm, __ldcg(p.part_ml + (base + sp) * 2));
+        float sum = 0.f, acc = 0.f;
+        for (int sp = 0; sp < live; ++sp) {
+            const float ms = __ldcg(p.part_ml + (base + sp) * 2);
+            if (ms == -INFINITY) continue;
+            const float f = exp2f(ms - mm);
+            sum += f * __ldcg(p.part_ml + (base + sp) * 2 + 1);
+            acc += f * __ldcg(p.part_o + (base + sp) * p.dv + c);
+        }
+        acc = sum > 0.f ? acc / sum : 0.f;
+        if (p.gate) acc *= logistic(__bfloat162float(p.gate[(size_t)token * p.gate_stride + (size_t)head * p.dv + c]));
+        p.out[(size_t)token * p.n_head * p.dv + (size_t)head * p.dv + c] = __float2bfloat16_rn(acc);
+    }
 }
 
 // out[token, head] = (sum over ranges of 2^(m_s - M) O_s) / (sum of 2^(m_s - M) l_s), times the gate.
@@ -434,14 +476,17 @@ __global__ void attention_merge_kernel(const AttnParams p) {
     const int token = blockIdx.x, head = blockIdx.y;
     const size_t base = ((size_t)token * p.n_head + head) * p.splits;
     bf16* orow = p.out + (size_t)token * p.n_head * p.dv + (size_t)head * p.dv;
-    if (p.positions[token] < 0) {
+    const int position = p.positions[token];
+    if (position < 0) {
         for (int c = threadIdx.x; c < p.dv; c += blockDim.x) orow[c] = __float2bfloat16_rn(0.f);
         return;
     }
+    const int lo_row = p.window > 0 ? max(0, position - p.window + 1) : 0;
+    const int live = min(p.splits, (position - (lo_row / KB) * KB) / p.split_keys + 1);   // ranges that hold keys
     float mm = -INFINITY;
-    for (int s = 0; s < p.splits; ++s) mm = fmaxf(mm, p.part_ml[(base + s) * 2]);
+    for (int s = 0; s < live; ++s) mm = fmaxf(mm, p.part_ml[(base + s) * 2]);
     float sum = 0.f;
-    for (int s = 0; s < p.splits; ++s) {
+    for (int s = 0; s < live; ++s) {
         const float ms = p.part_ml[(base + s) * 2];
         if (ms != -INFINITY) sum += exp2f(ms - mm) * p.part_ml[(base + s) * 2 + 1];
     }
@@ -449,7 +494,7 @@ __global__ void attention_merge_kernel(const AttnParams p) {
     const bf16* grow = p.gate ? p.gate + (size_t)token * p.gate_stride + (size_t)head * p.dv : nullptr;
     for (int c = threadIdx.x; c < p.dv; c += blockDim.x) {
         float acc = 0.f;
-        for (int s = 0; s < p.splits; ++s) {
+        for (int s = 0; s < live; ++s) {
             const float ms = p.part_ml[(base + s) * 2];
             if (ms != -INFINITY) acc += exp2f(ms - mm) * p.part_o[(base + s) * p.dv + c];
         }
@@ -469,7 +514,7 @@ int launch(const AttnParams& p, int single_tokens, int n_tiles, cudaStream_t s) 
         e = cudaFuncSetAttribute(attention_split_kernel<DP, DVP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e == cudaSuccess)
             e = mg_launch(attention_split_kernel<DP, DVP>, dim3(p.n_tokens, p.n_kv_head, p.splits), dim3(128), smem, s, true, p);
-        if (e == cudaSuccess)
+        if (e == cudaSuccess && p.counters == nullptr)
             e = mg_launch(attention_merge_kernel, dim3(p.n_tokens, p.n_head), dim3(p.dv >= 128 ? 128 : 64), 0, s, true, p);
     } else {
         e = cudaFuncSetAttribute(attention_tiles_kernel<DP, DVP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -496,12 +541,13 @@ MG_API long long mg_attention_mma_scratch_floats(int n_tokens, int n_head, int d
 // q: [n_tokens, q_stride] bfloat16 (heads of d features first); pages as in the general kernel;
 // gate: rows of gate_stride elements or null; out: [n_tokens, n_head * dv] bfloat16.
 // single_tokens = 1: every token is alone in its request's step (splits ranges of split_keys keys,
-// scratch of mg_attention_mma_scratch_floats floats); 0: n_tiles tiles of tile_tokens tokens, found
+// scratch of mg_attention_mma_scratch_floats floats; counters: n_tokens * n_kv_head zeros that are left
+// as zeros, or null to merge the ranges in a second kernel); 0: n_tiles tiles of tile_tokens tokens, found
 // from req_q_start / req_q_len.  Returns MG_ERR_UNSUPPORTED for sizes it does not take.
 MG_API int mg_attention_mma(const void* q, int q_stride, const void* k_pages, const void* v_pages, const int* block_table,
                             const int* token_request, const int* positions, const int* req_q_start,
                             const int* req_q_len, const void* gate, int gate_stride, void* out, float* scratch,
-                            int n_tokens, int n_requests, int n_head, int n_kv_head, int d, int dv, int page_tokens,
+                            int* counters, int n_tokens, int n_requests, int n_head, int n_kv_head, int d, int dv, int page_tokens,
                             int max_pages, int window, float scale, int num_pages, int single_tokens, int n_tiles,
                             int tile_tokens, int splits, int split_keys, void* stream) {
     if (n_tokens == 0) return MG_OK;
@@ -516,7 +562,7 @@ MG_API int mg_attention_mma(const void* q, int q_stride, const void* k_pages, co
     p.q = (const bf16*)q; p.q_stride = q_stride; p.k_pages = (const bf16*)k_pages; p.v_pages = (const bf16*)v_pages;
     p.block_table = block_table; p.token_request = token_request; p.positions = positions;
     p.req_q_start = req_q_start; p.req_q_len = req_q_len; p.gate = (const bf16*)gate; p.gate_stride = gate_stride;
-    p.out = (bf16*)out; p.part_o = nullptr; p.part_ml = nullptr;
+    p.out = (bf16*)out; p.part_o = nullptr; p.part_ml = nullptr; p.counters = single_tokens ? counters : nullptr;
     p.n_tokens = n_tokens; p.n_requests = n_requests; p.n_head = n_head; p.n_kv_head = n_kv_head; p.d = d; p.dv = dv;
     p.page_tokens = page_tokens; p.max_pages = max_pages; p.window = window > 0 ? window : 0; p.num_pages = num_pages;
     p.tile_tokens = tile_tokens; p.splits = splits; p.split_keys = split_keys; p.scale_log2 = scale * LOG2E;

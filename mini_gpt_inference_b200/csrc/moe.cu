@@ -260,8 +260,8 @@ moe_gemm_kernel(const T* __restrict__ x, int ldx, const T* __restrict__ w, long 
 // buffers (cp.async: the next tile's copies are in flight while this one is multiplied); four warps as
 // 2 x 2, each 32 slots x 64 matrix rows.  For the gated product a warp's 64 rows are 32 gate rows and
 // the 32 up rows of the same outputs, so silu(gate) * up happens in the accumulators.
-constexpr int MT = 64, MB = 128, MK = 64, MLD = MK + 8;
-constexpr size_t MOE_MMA_SMEM = (size_t)2 * (MT + MB) * MLD * sizeof(bf16);
+constexpr int MT = 64, MK = 64, MLD = MK + 8;
+constexpr size_t moe_mma_smem(int mb) { return (size_t)2 * (MT + mb) * MLD * sizeof(bf16); }
 
 __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -280,7 +280,10 @@ __device__ __forceinline__ void copy16_async(bf16* dst, const bf16* src, bool re
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
 }
 
-template <bool GLU>
+// MB: rows of the expert's matrix per tile: 128 (four warps as 2 x 2, each 32 slots x 64 rows), or 64 for
+// steps of few tokens (four warps as 4 x 1, each 16 slots x 64 rows): twice the CTAs, so that more of the
+// matrices is in flight when the work is nothing but reading them.
+template <bool GLU, int MB>
 __global__ void __launch_bounds__(128)
 moe_gemm_mma_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ w, long long w_expert_stride,
                     const int* __restrict__ offsets, const int* __restrict__ slot_entry, int top,
@@ -295,8 +298,10 @@ moe_gemm_mma_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
     const int first = offsets[e], count = offsets[e + 1] - first;
     const int m0 = blockIdx.y * MT;
     if (m0 >= count) return;
-    const int n0 = blockIdx.x * (GLU ? 64 : 128);
+    const int n0 = blockIdx.x * (GLU ? MB / 2 : MB);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    constexpr int MI = MB == 128 ? 2 : 1;                  // m16 tiles per warp
+    constexpr int BCH = MB * 8 / 128;                      // weight chunks per thread and tile
     if (tid < MT) {
         int r = -1;
         if (m0 + tid < count) {
@@ -308,9 +313,9 @@ moe_gemm_mma_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
     }
     __syncthreads();
     const bf16* we = w + (size_t)e * w_expert_stride;
-    // what this thread copies per tile: 4 chunks of 8 activations, 8 chunks of 8 weights
+    // what this thread copies per tile: 4 chunks of 8 activations, 8 or 4 chunks of 8 weights
     const bf16* a_src[4];
-    const bf16* b_src[8];
+    const bf16* b_src[BCH];
     const int chunk = (tid & 7) * 8;                       // the same column for all of a thread's chunks
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
@@ -318,7 +323,7 @@ moe_gemm_mma_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
         a_src[u] = row_of[row] >= 0 ? x + (size_t)row_of[row] * ldx + chunk : nullptr;
     }
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
+    for (int u = 0; u < BCH; ++u) {
         const int row = (tid + 128 * u) >> 3;
         int n, wrow;
         if (GLU) {
@@ -339,16 +344,17 @@ moe_gemm_mma_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
             copy16_async(as + buf * MT * MLD + ((tid + 128 * u) >> 3) * MLD + chunk, real ? a_src[u] + k0 : x, real);
         }
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
+        for (int u = 0; u < BCH; ++u) {
             const bool real = b_src[u] != nullptr && in_k;
             copy16_async(bs + buf * MB * MLD + ((tid + 128 * u) >> 3) * MLD + chunk, real ? b_src[u] + k0 : w, real);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    const int wr = warp >> 1, wc = warp & 1;
-    float acc[2][8][4];
+    const int wr = MB == 128 ? warp >> 1 : warp, wc = MB == 128 ? warp & 1 : 0;
+    const int m_warp = wr * 16 * MI;                       // the warp's first slot of the tile
+    float acc[MI][8][4];
 #pragma unroll
-    for (int i = 0; i < 2; ++i)
+    for (int i = 0; i < MI; ++i)
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
     const int iters = (K + MK - 1) / MK;
@@ -366,16 +372,16 @@ moe_gemm_mma_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
         const bf16* bt = bs + buf * MB * MLD;
 #pragma unroll
         for (int kk = 0; kk < MK / 16; ++kk) {
-            uint32_t af[2][4];
+            uint32_t af[MI][4];
 #pragma unroll
-            for (int i = 0; i < 2; ++i)
-                ldmatrix4(af[i], at + (wr * 32 + i * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * MLD + kk * 16 + (lane >> 4) * 8);
+            for (int i = 0; i < MI; ++i)
+                ldmatrix4(af[i], at + (m_warp + i * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * MLD + kk * 16 + (lane >> 4) * 8);
 #pragma unroll
             for (int j = 0; j < 8; j += 2) {
                 uint32_t bf[4];
                 ldmatrix4(bf, bt + (wc * 64 + j * 8 + (lane >> 4) * 8 + (lane & 7)) * MLD + kk * 16 + ((lane >> 3) & 1) * 8);
 #pragma unroll
-                for (int i = 0; i < 2; ++i) {
+                for (int i = 0; i < MI; ++i) {
                     mma_16816(acc[i][j], af[i], bf[0], bf[1]);
                     mma_16816(acc[i][j + 1], af[i], bf[2], bf[3]);
                 }
@@ -384,10 +390,10 @@ moe_gemm_mma_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
         __syncthreads();                                    // the buffer is free for the tile after the next
     }
 #pragma unroll
-    for (int i = 0; i < 2; ++i)
+    for (int i = 0; i < MI; ++i)
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
-            const int m = m0 + wr * 32 + i * 16 + (lane >> 2) + 8 * half;
+            const int m = m0 + m_warp + i * 16 + (lane >> 2) + 8 * half;
             if (m >= count) continue;
             const size_t slot = (size_t)first + m;
             if (GLU) {
@@ -446,8 +452,6 @@ __global__ void glu_kernel(const T* __restrict__ gu, const float* __restrict__ s
     if (scale != nullptr) v *= scale[n];
     out[i] = from_float<T>(v);
 }
-
-inline dim3 block128() { return dim3(128); }
 
 #define MG_LAUNCHED(e, name)                                                                 \
     do {                                                                                     \
@@ -508,21 +512,31 @@ MG_API int mg_moe_gemm(const void* x, int ldx, const void* w, const int* offsets
     const bool tensor_cores = is_bf16 && K % 8 == 0 && ldx % 8 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 &&
                               (uintptr_t)out % 4 == 0;
     if (tensor_cores) {
-        const dim3 tgrid(ceil_div(N, glu ? 64 : 128), ceil_div(max_rows, MT), n_experts);
+        const bool few = max_rows <= MT;                    // few tokens: narrower tiles, more CTAs
+        const int mb = few ? 64 : 128;
+        const dim3 tgrid(ceil_div(N, glu ? mb / 2 : mb), ceil_div(max_rows, MT), n_experts);
         static bool configured = false;
         if (!configured) {
-            e = cudaFuncSetAttribute(moe_gemm_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MOE_MMA_SMEM);
+            e = cudaFuncSetAttribute(moe_gemm_mma_kernel<true, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)moe_mma_smem(128));
             if (e == cudaSuccess)
-                e = cudaFuncSetAttribute(moe_gemm_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MOE_MMA_SMEM);
+                e = cudaFuncSetAttribute(moe_gemm_mma_kernel<false, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)moe_mma_smem(128));
             MG_LAUNCHED(e, "moe gemm (shared memory)");
             configured = true;
         }
-        if (glu)
-            e = mg_launch(moe_gemm_mma_kernel<true>, tgrid, block128(), MOE_MMA_SMEM, s, true, (const bf16*)x, ldx, (const bf16*)w, stride,
-                          offsets, slot_entry, top, scale, out, N, K, x_rows);
+        const bf16* xb = (const bf16*)x;
+        const bf16* wb = (const bf16*)w;
+        if (glu && few)
+            e = mg_launch(moe_gemm_mma_kernel<true, 64>, tgrid, dim3(128), moe_mma_smem(64), s, true, xb, ldx, wb, stride, offsets,
+                          slot_entry, top, scale, out, N, K, x_rows);
+        else if (glu)
+            e = mg_launch(moe_gemm_mma_kernel<true, 128>, tgrid, dim3(128), moe_mma_smem(128), s, true, xb, ldx, wb, stride, offsets,
+                          slot_entry, top, scale, out, N, K, x_rows);
+        else if (few)
+            e = mg_launch(moe_gemm_mma_kernel<false, 64>, tgrid, dim3(128), moe_mma_smem(64), s, true, xb, ldx, wb, stride, offsets,
+                          slot_entry, top, scale, out, N, K, x_rows);
         else
-            e = mg_launch(moe_gemm_mma_kernel<false>, tgrid, block128(), MOE_MMA_SMEM, s, true, (const bf16*)x, ldx, (const bf16*)w,
-                          stride, offsets, slot_entry, top, scale, out, N, K, x_rows);
+            e = mg_launch(moe_gemm_mma_kernel<false, 128>, tgrid, dim3(128), moe_mma_smem(128), s, true, xb, ldx, wb, stride, offsets,
+                          slot_entry, top, scale, out, N, K, x_rows);
     } else if (is_bf16 && glu)
         e = mg_launch(moe_gemm_kernel<bf16, true>, grid, block, 0, s, true, (const bf16*)x, ldx, (const bf16*)w, stride,
                       offsets, slot_entry, top, scale, out, N, K, x_rows);

@@ -26,7 +26,7 @@ _SIGNATURES = {
     "mg_head_prepare": [_P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P],
     "mg_paged_attention_general": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _I, _I, _I, _F,
                                    _I, _I, _I, _P],
-    "mg_attention_mma": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F,
+    "mg_attention_mma": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F,
                          _I, _I, _I, _I, _I, _I, _P],
     "mg_moe_route": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "mg_moe_group": [_P, _I, _I, _P, _P, _P, _P],

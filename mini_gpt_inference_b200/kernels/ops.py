@@ -94,6 +94,7 @@ class CudaOps:
         self.use_dependent_launch = True
         self.use_prefill_tc = True
         self.use_mma_attention = True
+        self.merge_ranges_in_last_cta = False
         self._counter_buf = None
         self._retired_counters = []
         self._sm_count = None
@@ -704,21 +705,24 @@ class CudaOps:
                 splits = max(1, -(-int(ctx.max_ctx_after) // keys))
                 floats = self.lib.mg_attention_mma_scratch_floats(n, n_head, v_dim, splits)
                 scratch = torch.empty((floats,), dtype=torch.float32, device=self.device)
-                args = [_ptr(scratch), 1, 0, 1, splits, keys]
+                # (measured at batch 8, context 2,048: the ranges merged by a second kernel, 0.273 ms a
+                # step; by the last CTA of each token and key/value head, 0.283 ms)
+                counters = self._counters(n * n_kv_head) if self.merge_ranges_in_last_cta else None
+                args = [_ptr(scratch), _ptr(counters), 1, 0, 1, splits, keys]
             elif q_len and group <= 64 and getattr(ctx, "req_q_start", None) is not None:
                 tile = max(1, 64 // group)
-                args = [None, 0, sum(-(-int(t) // tile) for t in q_len), tile, 0, 0]
+                args = [None, None, 0, sum(-(-int(t) // tile) for t in q_len), tile, 0, 0]
             if args is not None:
                 code = self.lib.mg_attention_mma(
                     _ptr(q), q.shape[1], _ptr(cache.k_pages), _ptr(cache.v_pages), _ptr(table), _ptr(ctx.token_request),
                     _ptr(ctx.positions), _ptr(getattr(ctx, "req_q_start", None)), _ptr(getattr(ctx, "req_q_len", None)),
-                    _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(out), args[0], n, table.shape[0],
+                    _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(out), args[0], args[1], n, table.shape[0],
                     n_head, n_kv_head, head_dim, v_dim, cache.page_tokens, table.shape[1], int(cache.window or 0),
-                    float(scale), cache.k_pages.shape[0], *args[1:], self._stream())
+                    float(scale), cache.k_pages.shape[0], *args[2:], self._stream())
                 if code != library.UNSUPPORTED:
                     self._run(code, "paged_attention (tensor cores, general)")
-                    if single:
-                        self.launches += 1                       # the merge of the ranges
+                    if single and args[1] is None:
+                        self.launches += 1                       # the merge of the ranges as a kernel of its own
                     return out
         self._run(self.lib.mg_paged_attention_general(
             _ptr(q), q.shape[1], _ptr(cache.k_pages), _ptr(cache.v_pages), _ptr(table), _ptr(ctx.token_request),
