@@ -74,7 +74,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const int* __restrict__ block_table, const int* __restrict__ positions,
                             bf16* __restrict__ out, float* __restrict__ partial, int* __restrict__ counters,
                             int n_head, int n_kv_head, int page_tokens, int box_rows, int max_pages, int window,
-                            float scale_log2e, int* __restrict__ status, int n_tokens, int num_pages, int n_requests) {
+                            float scale_log2e, int* __restrict__ status, int n_tokens, int num_pages, int n_requests,
+                            const bf16* __restrict__ gate, int gate_stride) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t pad = (1024u - (smem_u32(smem_raw) & 1023u)) & 1023u;
     if (pad > ALIGN_SLACK) {                           // uniform over the CTA; nothing is held yet
@@ -375,13 +376,23 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (tid < n_rows) {
             const float inv = run_sum > 0.f ? 1.0f / run_sum : 0.f;
             uint4* dst = reinterpret_cast<uint4*>(out + ((size_t)(row0 + tid) * n_head + head) * D);
+            // an output gate: every feature times the logistic function of its gate value
+            const uint4* grow = gate ? reinterpret_cast<const uint4*>(gate + (size_t)(row0 + tid) * gate_stride + (size_t)head * D) : nullptr;
 #pragma unroll
             for (int c = 0; c < D / 8; ++c) {
                 uint32_t packed[4];
+                uint4 g4 = make_uint4(0u, 0u, 0u, 0u);
+                if (grow) g4 = grow[c];
+                const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w};
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(o[c * 8 + 2 * j]) * inv,
-                                                                   __uint_as_float(o[c * 8 + 2 * j + 1]) * inv);
+                    float a = __uint_as_float(o[c * 8 + 2 * j]) * inv, b = __uint_as_float(o[c * 8 + 2 * j + 1]) * inv;
+                    if (grow) {
+                        const __nv_bfloat162 g2 = *reinterpret_cast<const __nv_bfloat162*>(&gw[j]);
+                        a *= 1.0f / (1.0f + __expf(-__bfloat162float(g2.x)));
+                        b *= 1.0f / (1.0f + __expf(-__bfloat162float(g2.y)));
+                    }
+                    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
                     packed[j] = *reinterpret_cast<const uint32_t*>(&h);
                 }
                 dst[c] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
@@ -430,12 +441,22 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
             const float inv = denom > 0.f ? 1.0f / denom : 0.f;
             uint4* dst = reinterpret_cast<uint4*>(out + ((size_t)(row0 + tid) * n_head + head) * D);
+            const uint4* grow = gate ? reinterpret_cast<const uint4*>(gate + (size_t)(row0 + tid) * gate_stride + (size_t)head * D) : nullptr;
 #pragma unroll
             for (int c = 0; c < D / 8; ++c) {
                 uint32_t packed[4];
+                uint4 g4 = make_uint4(0u, 0u, 0u, 0u);
+                if (grow) g4 = grow[c];
+                const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w};
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const __nv_bfloat162 h = __floats2bfloat162_rn(acc[c * 8 + 2 * j] * inv, acc[c * 8 + 2 * j + 1] * inv);
+                    float a = acc[c * 8 + 2 * j] * inv, b = acc[c * 8 + 2 * j + 1] * inv;
+                    if (grow) {
+                        const __nv_bfloat162 g2 = *reinterpret_cast<const __nv_bfloat162*>(&gw[j]);
+                        a *= 1.0f / (1.0f + __expf(-__bfloat162float(g2.x)));
+                        b *= 1.0f / (1.0f + __expf(-__bfloat162float(g2.y)));
+                    }
+                    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
                     packed[j] = *reinterpret_cast<const uint32_t*>(&h);
                 }
                 dst[c] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
@@ -496,6 +517,9 @@ MG_API long long mg_attention_prefill_scratch_floats(int n_items, int n_head) {
 // part `chunk`; the items of one tile are consecutive, chunk 0 first.  If any tile is cut
 // (merge != 0), `partial` holds mg_attention_prefill_scratch_floats() floats and `counters`
 // n_items * n_head ints that are zero before the call and zero again after it.
+// q_stride: elements per row of qkv if the rows are wider than q, k, v of 64 features each (0: exactly
+// that); gate: rows of gate_stride elements whose first n_head * 64 are gate values (the output is
+// multiplied by their logistic function), or null.
 // qkv: [n_tokens, (n_head + 2 n_kv_head) * 64] bf16; pages: [num_pages, n_kv_head, page_tokens, 64];
 // out: [n_tokens, n_head * 64]; n_requests: rows of the block table (guarded builds hold the work
 // items' request numbers against it).  Returns MG_ERR_UNSUPPORTED unless head_dim is 64 and page_tokens
@@ -505,7 +529,7 @@ MG_API int mg_attention_prefill_tc(const void* qkv, const void* k_pages, const v
                                    int* counters, int merge, int n_items,
                                    int n_tokens, int n_head, int n_kv_head, int head_dim, int page_tokens,
                                    long long num_pages, int max_pages, int window, float scale, int n_requests,
-                                   int* status, void* stream) {
+                                   int q_stride, const void* gate, int gate_stride, int* status, void* stream) {
     if (n_items == 0) return MG_OK;
     MG_REQUIRE(n_items > 0 && n_tokens > 0 && n_head > 0 && n_kv_head > 0 && page_tokens > 0 && max_pages > 0 && status,
                "attention (prefill): bad arguments");
@@ -516,7 +540,10 @@ MG_API int mg_attention_prefill_tc(const void* qkv, const void* k_pages, const v
     if (head_dim != D || !pages_ok || n_head > 65535 || (((uintptr_t)qkv | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15))
         return mg_set_error(MG_ERR_UNSUPPORTED, "attention (prefill, tensor cores): needs head_dim 64 and a page size of 8..128 dividing 128 or a multiple of 128");
     const int box_rows = page_tokens < BK ? page_tokens : BK;
-    const int qkv_width = (n_head + 2 * n_kv_head) * D;
+    const int qkv_width = q_stride > 0 ? q_stride : (n_head + 2 * n_kv_head) * D;
+    if (qkv_width < n_head * D || qkv_width % 8 != 0 ||
+        (gate != nullptr && (gate_stride % 8 != 0 || gate_stride < n_head * D || ((uintptr_t)gate & 15))))
+        return mg_set_error(MG_ERR_UNSUPPORTED, "attention (prefill, tensor cores): rows and gate must be 16-byte aligned");
     CUtensorMap map_q, map_k, map_v;
     int rc = make_map(qkv, n_tokens, qkv_width, BQ, &map_q);
     if (rc != MG_OK) return rc;
@@ -536,7 +563,7 @@ MG_API int mg_attention_prefill_tc(const void* qkv, const void* k_pages, const v
     cudaError_t le = mg_launch(attention_prefill_tc_kernel, grid, dim3(THREADS), smem, (cudaStream_t)stream, true, map_q,
                                map_k, map_v, work, block_table, positions, (bf16*)out, partial, counters, n_head, n_kv_head,
                                page_tokens, box_rows, max_pages, window, scale * 1.4426950408889634f, status, n_tokens,
-                               (int)num_pages, n_requests);
+                               (int)num_pages, n_requests, (const bf16*)gate, gate_stride);
     if (le != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "attention_prefill_tc: %s", cudaGetErrorString(le));
     MG_CHECK_LAUNCH("attention_prefill_tc");
     return MG_OK;

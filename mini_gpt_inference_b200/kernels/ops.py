@@ -640,7 +640,7 @@ class CudaOps:
                 _ptr(ctx.positions), _ptr(out), _ptr(partial), _ptr(counters), merge, work.shape[0], n, n_head,
                 n_kv_head, head_dim,
                 cache.page_tokens, cache.k_pages.shape[0], table.shape[1], window, float(scale),
-                table.shape[0], _ptr(self.status), self._stream())
+                table.shape[0], 0, None, 0, _ptr(self.status), self._stream())
             if code != library.UNSUPPORTED:
                 self._run(code, "paged_attention (prefill, tensor cores)")
                 return out
@@ -693,6 +693,27 @@ class CudaOps:
                                  or gate.shape != (n, n_head * v_dim)):
             raise KernelLibraryError("attention: the gate does not fit the heads")
         out = torch.empty((n, n_head * v_dim), dtype=q.dtype, device=self.device)
+        work = getattr(ctx, "extra", {}).get(self._attention_tiles_name(n_head)) if hasattr(ctx, "extra") else None
+        if (q.dtype == torch.bfloat16 and work is not None and work.shape[0] > 0 and head_dim == v_dim
+                and head_dim in self.PREFILL_TC_HEAD_DIMS and self.use_tensor_cores and self.use_prefill_tc
+                and not getattr(ctx, "decode_only", False)):
+            # equal key and value sizes that the tcgen05 prompt attention takes: its tiles, with the
+            # rows' own width and the gate in its epilogue
+            merge = int(ctx.max_ctx_after > KEY_CHUNK)
+            partial = counters = None
+            if merge:
+                floats = self.lib.mg_attention_prefill_scratch_floats(work.shape[0], n_head)
+                partial = torch.empty((floats,), dtype=torch.float32, device=self.device)
+                counters = self._counters(work.shape[0] * n_head)
+            code = self.lib.mg_attention_prefill_tc(
+                _ptr(q), _ptr(cache.k_pages), _ptr(cache.v_pages), _ptr(work), _ptr(table), _ptr(ctx.positions),
+                _ptr(out), _ptr(partial), _ptr(counters), merge, work.shape[0], n, n_head, n_kv_head, head_dim,
+                cache.page_tokens, cache.k_pages.shape[0], table.shape[1], int(cache.window or 0), float(scale),
+                table.shape[0], q.shape[1], _ptr(gate), gate.stride(0) if gate is not None else 0,
+                _ptr(self.status), self._stream())
+            if code != library.UNSUPPORTED:
+                self._run(code, "paged_attention (prefill, tensor cores)")
+                return out
         if q.dtype == torch.bfloat16 and self.use_tensor_cores and self.use_mma_attention:
             # bfloat16: tiles of (token, head) rows on the warp-level tensor cores; single tokens
             # with their keys cut into ranges that a second kernel merges

@@ -104,6 +104,13 @@ class GatedUnitAttention(Mixer):
                            self.cache_pages,
                            None if self.v_head_dim == self.head_dim else self.v_head_dim)
 
+    def plan_step(self, batch, plan, ops) -> None:
+        # where keys and values have one size, the kernel set may cut prompt portions into the tiles of
+        # its tiled attention kernel (the same work list as the plain causal attention's)
+        planner = getattr(ops, "plan_prompt_attention", None)
+        if planner is not None and self.head_dim == self.v_head_dim:
+            planner(batch, plan, self.n_head, self.n_kv_head, self.head_dim)
+
     def forward(self, ctx, cache, y, residual32) -> None:
         ops = ctx.ops
         proj = ops.linear(y, self.fused_weight, None, "none", ctx.act_dtype)

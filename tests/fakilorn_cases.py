@@ -40,7 +40,8 @@ def config(which: str, sharp: float = 1.0, every_expert: bool = False) -> dict:
 def _config(which: str, sharp: float) -> dict:
     """A: grouped heads, keys larger than values, a blending chain that starts at the second layer,
     every kind of feed-forward.  B: as many key heads as query heads, equal key and value sizes, one
-    chosen expert, all experts chosen, no shared expert.  C: sizes that are multiples of nothing."""
+    chosen expert, all experts chosen, no shared expert.  C: sizes that are multiples of nothing.  D: keys
+    and values of 64 features."""
     if which == "A":
         layers = [
             {"type": "attention", "mixer": _attn(4, 2, 24, 16, False, sharp), "mlp": {"kind": "dense", "ff": 96}},
@@ -65,10 +66,18 @@ def _config(which: str, sharp: float) -> dict:
         ]
         return {"architecture": "Fakilorn", "vocab": 97, "width": 50, "layers": layers,
                 "embedding": {"scale": 3.0}, "logit_scale": 0.37, "norm": {"eps": 1e-5}}
+    if which == "D":
+        # keys and values of 64 features each: the sizes that the tcgen05 prompt attention takes
+        layers = [
+            {"type": "attention", "mixer": _attn(4, 2, 64, 64, True, sharp), "mlp": {"kind": "dense", "ff": 160}},
+            {"type": "attention", "mixer": _attn(4, 2, 64, 64, True, sharp), "mlp": _moe(4, 2, 64, 32)},
+        ]
+        return {"architecture": "Fakilorn", "vocab": 173, "width": 128, "layers": layers,
+                "embedding": {"scale": 1.3}, "logit_scale": 0.9, "norm": {"eps": 1e-5}}
     raise KeyError(which)
 
 
-PAGE_TOKENS = {"A": 16, "B": 8, "C": 4}
+PAGE_TOKENS = {"A": 16, "B": 8, "C": 4, "D": 16}
 
 
 def tensor_shapes(cfg: dict) -> dict[str, tuple]:

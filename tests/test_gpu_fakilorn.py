@@ -244,7 +244,7 @@ def test_scaled_embedding_and_head(ops):
 
 
 # ---- the step function --------------------------------------------------------------------------
-CASES = [(w, d, s) for w in "ABC" for d in ("float32", "bfloat16") for s in (1.0, 4.0)]
+CASES = [(w, d, s) for w in "ABCD" for d in ("float32", "bfloat16") for s in (1.0, 4.0)]
 IDS = [f"{w}-{d}-{'sharp' if s > 1 else 'soft'}" for w, d, s in CASES]
 
 
@@ -260,9 +260,9 @@ def setup(which, dtype, sharp, num_pages=64, seed=3, max_requests=4):
 
 @pytest.mark.parametrize("which,dtype,sharp", CASES, ids=IDS)
 def test_whole_prompts(which, dtype, sharp):
-    raw, tensors, runner, tol = setup(which, dtype, sharp)
+    raw, tensors, runner, tol = setup(which, dtype, sharp, num_pages=400)
     pt = PAGE_TOKENS[which]
-    for length, seed in [(150, 1), (37, 2), (1, 3), (2, 4), (pt + 1, 5), (pt, 6)]:
+    for length, seed in [(150, 1), (37, 2), (1, 3), (2, 4), (pt + 1, 5), (pt, 6), (1300, 7)]:
         tokens = tokens_for(raw, length, seed)
         got = runner.step([StepEntry("r", tokens, list(range(length)))])
         runner.finish("r")
