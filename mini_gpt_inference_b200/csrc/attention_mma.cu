@@ -12,6 +12,7 @@
 //          group's heads, 16 rows per warp; every warp walks every key block.  The CTA finds its
 //          request and tile from the requests' token counts on the device.
 //   split  (single tokens): a CTA is one token, one key/value head and one range of keys; the
+//          (128 keys unless the longest possible context would need more than 1,024 ranges); the
 //          group's heads are the rows of one m16 tile, each warp takes 16 of a block's 64 keys, the
 //          warps' partial results meet in shared memory and go to scratch; the CTA that finishes a
 //          (token, key/value head) last merges the ranges, applies the gate and stores (or a second
@@ -529,8 +530,11 @@ int launch(const AttnParams& p, int single_tokens, int n_tiles, cudaStream_t s) 
 
 // Ranges of keys per token for contexts of up to max_context keys, and the keys per range.
 MG_API int mg_attention_mma_split_keys(int max_context) {
-    int keys = 256;
-    while ((max_context + keys - 1) / keys > 64) keys *= 2;
+    // short ranges: many CTAs with two blocks each (a CTA's blocks follow one another at a memory
+    // round trip apiece); ranges beyond a token's own context leave at once, so the count only sizes
+    // the grid and the scratch
+    int keys = 128;
+    while ((max_context + keys - 1) / keys > 1024) keys *= 2;
     return keys;
 }
 
