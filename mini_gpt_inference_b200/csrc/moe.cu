@@ -261,7 +261,7 @@ moe_gemm_kernel(const T* __restrict__ x, int ldx, const T* __restrict__ w, long 
 // 2 x 2, each 32 slots x 64 matrix rows.  For the gated product a warp's 64 rows are 32 gate rows and
 // the 32 up rows of the same outputs, so silu(gate) * up happens in the accumulators.
 constexpr int MT = 64, MK = 64, MLD = MK + 8;
-constexpr size_t moe_mma_smem(int mb) { return (size_t)2 * (MT + mb) * MLD * sizeof(bf16); }
+constexpr size_t moe_mma_smem(int mb, int stages) { return (size_t)stages * (MT + mb) * MLD * sizeof(bf16); }
 
 __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -283,14 +283,16 @@ __device__ __forceinline__ void copy16_async(bf16* dst, const bf16* src, bool re
 // MB: rows of the expert's matrix per tile: 128 (four warps as 2 x 2, each 32 slots x 64 rows), or 64 for
 // steps of few tokens (four warps as 4 x 1, each 16 slots x 64 rows): twice the CTAs, so that more of the
 // matrices is in flight when the work is nothing but reading them.
-template <bool GLU, int MB>
+// NS: shared-memory buffers that take turns (NS - 1 tiles are in flight while one is multiplied): two
+// where many CTAs share an SM, four where a CTA does little but wait for its matrix.
+template <bool GLU, int MB, int NS>
 __global__ void __launch_bounds__(128)
 moe_gemm_mma_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ w, long long w_expert_stride,
                     const int* __restrict__ offsets, const int* __restrict__ slot_entry, int top,
                     const float* __restrict__ scale, void* __restrict__ out, int N, int K, int x_rows) {
     extern __shared__ __align__(16) uint8_t moe_smem[];
-    bf16* as = reinterpret_cast<bf16*>(moe_smem);          // [2][MT * MLD]
-    bf16* bs = as + 2 * MT * MLD;                          // [2][MB * MLD]
+    bf16* as = reinterpret_cast<bf16*>(moe_smem);          // [NS][MT * MLD]
+    bf16* bs = as + NS * MT * MLD;                         // [NS][MB * MLD]
     __shared__ int row_of[MT];
     pdl_trigger();
     pdl_wait();
@@ -358,15 +360,18 @@ moe_gemm_mma_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
     const int iters = (K + MK - 1) / MK;
-    issue(0, 0);
+    // one group of copies per tile, also beyond the last tile (then empty), so that "all but the
+    // newest NS - 1 groups have landed" always means: this iteration's tile is there
+#pragma unroll
+    for (int st = 0; st < NS - 1; ++st) {
+        if (st < iters) issue(st, st * MK);
+        else asm volatile("cp.async.commit_group;" ::: "memory");
+    }
     for (int it = 0; it < iters; ++it) {
-        const int buf = it & 1;
-        if (it + 1 < iters) {
-            issue(buf ^ 1, (it + 1) * MK);                  // in flight while this tile is multiplied
-            asm volatile("cp.async.wait_group 1;" ::: "memory");
-        } else {
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-        }
+        const int buf = it % NS;
+        if (it + NS - 1 < iters) issue((it + NS - 1) % NS, (it + NS - 1) * MK);
+        else asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group %0;" ::"n"(NS - 1) : "memory");
         __syncthreads();
         const bf16* at = as + buf * MT * MLD;
         const bf16* bt = bs + buf * MB * MLD;
@@ -387,7 +392,7 @@ moe_gemm_mma_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
                 }
             }
         }
-        __syncthreads();                                    // the buffer is free for the tile after the next
+        __syncthreads();                                    // the buffer is free for a later tile
     }
 #pragma unroll
     for (int i = 0; i < MI; ++i)
@@ -517,26 +522,30 @@ MG_API int mg_moe_gemm(const void* x, int ldx, const void* w, const int* offsets
         const dim3 tgrid(ceil_div(N, glu ? mb / 2 : mb), ceil_div(max_rows, MT), n_experts);
         static bool configured = false;
         if (!configured) {
-            e = cudaFuncSetAttribute(moe_gemm_mma_kernel<true, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)moe_mma_smem(128));
+            e = cudaFuncSetAttribute(moe_gemm_mma_kernel<true, 128, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)moe_mma_smem(128, 2));
             if (e == cudaSuccess)
-                e = cudaFuncSetAttribute(moe_gemm_mma_kernel<false, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)moe_mma_smem(128));
+                e = cudaFuncSetAttribute(moe_gemm_mma_kernel<false, 128, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)moe_mma_smem(128, 2));
+            if (e == cudaSuccess)
+                e = cudaFuncSetAttribute(moe_gemm_mma_kernel<true, 64, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)moe_mma_smem(64, 4));
+            if (e == cudaSuccess)
+                e = cudaFuncSetAttribute(moe_gemm_mma_kernel<false, 64, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)moe_mma_smem(64, 4));
             MG_LAUNCHED(e, "moe gemm (shared memory)");
             configured = true;
         }
         const bf16* xb = (const bf16*)x;
         const bf16* wb = (const bf16*)w;
         if (glu && few)
-            e = mg_launch(moe_gemm_mma_kernel<true, 64>, tgrid, dim3(128), moe_mma_smem(64), s, true, xb, ldx, wb, stride, offsets,
-                          slot_entry, top, scale, out, N, K, x_rows);
+            e = mg_launch(moe_gemm_mma_kernel<true, 64, 4>, tgrid, dim3(128), moe_mma_smem(64, 4), s, true, xb, ldx, wb, stride,
+                          offsets, slot_entry, top, scale, out, N, K, x_rows);
         else if (glu)
-            e = mg_launch(moe_gemm_mma_kernel<true, 128>, tgrid, dim3(128), moe_mma_smem(128), s, true, xb, ldx, wb, stride, offsets,
-                          slot_entry, top, scale, out, N, K, x_rows);
+            e = mg_launch(moe_gemm_mma_kernel<true, 128, 2>, tgrid, dim3(128), moe_mma_smem(128, 2), s, true, xb, ldx, wb, stride,
+                          offsets, slot_entry, top, scale, out, N, K, x_rows);
         else if (few)
-            e = mg_launch(moe_gemm_mma_kernel<false, 64>, tgrid, dim3(128), moe_mma_smem(64), s, true, xb, ldx, wb, stride, offsets,
-                          slot_entry, top, scale, out, N, K, x_rows);
+            e = mg_launch(moe_gemm_mma_kernel<false, 64, 4>, tgrid, dim3(128), moe_mma_smem(64, 4), s, true, xb, ldx, wb, stride,
+                          offsets, slot_entry, top, scale, out, N, K, x_rows);
         else
-            e = mg_launch(moe_gemm_mma_kernel<false, 128>, tgrid, dim3(128), moe_mma_smem(128), s, true, xb, ldx, wb, stride, offsets,
-                          slot_entry, top, scale, out, N, K, x_rows);
+            e = mg_launch(moe_gemm_mma_kernel<false, 128, 2>, tgrid, dim3(128), moe_mma_smem(128, 2), s, true, xb, ldx, wb, stride,
+                          offsets, slot_entry, top, scale, out, N, K, x_rows);
     } else if (is_bf16 && glu)
         e = mg_launch(moe_gemm_kernel<bf16, true>, grid, block, 0, s, true, (const bf16*)x, ldx, (const bf16*)w, stride,
                       offsets, slot_entry, top, scale, out, N, K, x_rows);
