@@ -471,7 +471,13 @@ attention_split_kernel(const AttnParams p) {
 }
 
 // out[token, head] = (sum over ranges of 2^(m_s - M) O_s) / (sum of 2^(m_s - M) l_s), times the gate.
+// The ranges' maxima and sums come to shared memory in one trip, their weights are worked out there
+// once, and every thread then sums its column over the ranges with independent loads.
+constexpr int MERGE_MAX = 1024;   // most ranges (mg_attention_mma_split_keys keeps to it)
+
 __global__ void attention_merge_kernel(const AttnParams p) {
+    __shared__ float weight[MERGE_MAX];
+    __shared__ float norm;
     pdl_trigger();
     pdl_wait();
     const int token = blockIdx.x, head = blockIdx.y;
@@ -483,23 +489,30 @@ __global__ void attention_merge_kernel(const AttnParams p) {
         return;
     }
     const int lo_row = p.window > 0 ? max(0, position - p.window + 1) : 0;
-    const int live = min(p.splits, (position - (lo_row / KB) * KB) / p.split_keys + 1);   // ranges that hold keys
-    float mm = -INFINITY;
-    for (int s = 0; s < live; ++s) mm = fmaxf(mm, p.part_ml[(base + s) * 2]);
-    float sum = 0.f;
-    for (int s = 0; s < live; ++s) {
-        const float ms = p.part_ml[(base + s) * 2];
-        if (ms != -INFINITY) sum += exp2f(ms - mm) * p.part_ml[(base + s) * 2 + 1];
+    const int live = min(min(p.splits, MERGE_MAX), (position - (lo_row / KB) * KB) / p.split_keys + 1);   // ranges that hold keys
+    for (int s = threadIdx.x; s < live; s += blockDim.x) weight[s] = p.part_ml[(base + s) * 2];
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float mm = -INFINITY;
+        for (int s = threadIdx.x; s < live; s += 32) mm = fmaxf(mm, weight[s]);
+        mm = warp_max(mm);
+        float sum = 0.f;
+        for (int s = threadIdx.x; s < live; s += 32) {
+            const float ms = weight[s];
+            const float w = ms == -INFINITY ? 0.f : exp2f(ms - mm);
+            weight[s] = w;
+            sum += w * p.part_ml[(base + s) * 2 + 1];
+        }
+        sum = warp_sum(sum);
+        if (threadIdx.x == 0) norm = sum > 0.f ? 1.0f / sum : 0.f;
     }
-    const float inv = sum > 0.f ? 1.0f / sum : 0.f;
+    __syncthreads();
     const bf16* grow = p.gate ? p.gate + (size_t)token * p.gate_stride + (size_t)head * p.dv : nullptr;
     for (int c = threadIdx.x; c < p.dv; c += blockDim.x) {
         float acc = 0.f;
-        for (int s = 0; s < live; ++s) {
-            const float ms = p.part_ml[(base + s) * 2];
-            if (ms != -INFINITY) acc += exp2f(ms - mm) * p.part_o[(base + s) * p.dv + c];
-        }
-        acc *= inv;
+#pragma unroll 8
+        for (int s = 0; s < live; ++s) acc = fmaf(weight[s], p.part_o[(base + s) * p.dv + c], acc);
+        acc *= norm;
         if (grow) acc *= logistic(__bfloat162float(grow[c]));
         orow[c] = __float2bfloat16_rn(acc);
     }

@@ -30,6 +30,7 @@ __device__ __forceinline__ float route_dot(const T* __restrict__ row, const floa
                                            bool vec) {
     float dot = 0.f;
     if (vec) {
+#pragma unroll 4
         for (int c = lane * 4; c < width; c += 128) {
             const float4 wv = *reinterpret_cast<const float4*>(wr + c);
             dot = fmaf(to_float(row[c]), wv.x, dot);
