@@ -104,7 +104,7 @@ def test_unit_norm_blend_and_page_write(ops, dtype, heads, groups, d, dv):
 @pytest.mark.parametrize("dtype,path", [("float32", "general"), ("bfloat16", "general"), ("bfloat16", "tiles"),
                                         ("bfloat16", "ranges")])
 @pytest.mark.parametrize("heads,groups,d,dv,pt", [(4, 2, 24, 16, 8), (3, 3, 32, 32, 16), (6, 1, 10, 70, 4),
-                                                  (8, 2, 96, 64, 16), (16, 1, 128, 128, 32), (5, 5, 72, 104, 8)])
+                                                  (8, 2, 96, 32, 16), (16, 1, 128, 128, 32), (5, 5, 72, 104, 8)])
 def test_attention_far_key_gate_and_sizes(ops, dtype, path, heads, groups, d, dv, pt):
     """Two requests on scattered pages.  Every query is made to point at one key far back (or, for the
     second request, at the key of a page's last row): with a large scale nearly all weight lies
