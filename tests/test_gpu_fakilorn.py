@@ -174,6 +174,56 @@ def test_attention_far_key_gate_and_sizes(ops, dtype, path, heads, groups, d, dv
     assert torch.allclose(got.double().cpu(), gated, atol=tol, rtol=tol)
 
 
+@pytest.mark.parametrize("dtype,path", [("float32", "general"), ("bfloat16", "general"), ("bfloat16", "tiles"),
+                                        ("bfloat16", "ranges")])
+@pytest.mark.parametrize("window,pt", [(40, 8), (64, 16), (129, 4)])
+def test_attention_window_edges(ops, dtype, path, window, pt):
+    """A window of the last `window` keys (a parameter of the mixer that this design leaves unused):
+    the key just outside the window is made the most attractive of all, the first key inside it the
+    second most; a kernel that is one key off at either edge gives another row."""
+    t = DTYPES[dtype]
+    heads, groups, d, dv, length = 4, 2, 32, 48, 300
+    gen = torch.Generator().manual_seed(window)
+    n_pages = -(-length // pt)
+    order = torch.randperm(n_pages + 2, generator=gen).tolist()
+    tables = [order[:n_pages]]
+    k_all = torch.randn(length, groups, d, generator=gen)
+    v_all = torch.randn(length, groups, dv, generator=gen)
+    positions = list(range(length - 24, length))
+    direction = torch.randn(groups, d, generator=gen)
+    for p in positions:                                         # (edges of neighbouring queries overlap: the
+        k_all[p - window] = 4.0 * direction                     #  later assignment wins, the oracle sees the same)
+        k_all[p - window + 1] = 3.0 * direction
+    k_pages = torch.full((len(order), groups, pt, d), float("nan"))
+    v_pages = torch.full((len(order), groups, pt, dv), float("nan"))
+    for j in range(length):
+        k_pages[tables[0][j // pt], :, j % pt] = k_all[j]
+        v_pages[tables[0][j // pt], :, j % pt] = v_all[j]
+    n = len(positions)
+    q = (0.2 * torch.randn(n, heads, d, generator=gen)
+         + direction.repeat_interleave(heads // groups, 0)[None]).reshape(n, -1).to(t)
+    cache = PagedKVView(dev(k_pages, t), dev(v_pages, t), 0, pt, window, False)
+    ctx = Ctx(tables, [0] * n, positions, [n], decode_only=path == "ranges")
+    ops.use_mma_attention = path != "general"
+    try:
+        got = ops.paged_attention_general(dev(q), heads, groups, d, dv, 1.0 / math.sqrt(d), cache, ctx)
+    finally:
+        ops.use_mma_attention = True
+    want = torch.empty(n, heads, dv, dtype=torch.float64)
+    inside = []
+    for i, p in enumerate(positions):
+        lo = p - window + 1
+        for h in range(heads):
+            g = h // (heads // groups)
+            s = (k_all[lo: p + 1, g].to(t).double() @ q[i, h * d: (h + 1) * d].double()) / math.sqrt(d)
+            w = torch.softmax(s, 0)
+            inside.append(float(w[0]))
+            want[i, h] = w @ v_all[lo: p + 1, g].to(t).double()
+    assert max(inside) > 0.3                                    # the first key inside the window matters
+    tol = 2e-5 if dtype == "float32" else 3e-2
+    assert torch.allclose(got.double().cpu(), want.view(n, -1), atol=tol, rtol=tol)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("m,n,k", [(1, 96, 64), (9, 37, 50), (40, 200, 96), (150, 256, 64), (300, 96, 256)])
 def test_squared_relu_projection(ops, dtype, m, n, k):
@@ -438,3 +488,29 @@ def test_trace_replay(tmp_path):
         for step, rows in want.items():
             got = torch.from_numpy(np.fromfile(out / f"{step}.f32", dtype="<f4").reshape(len(rows), raw["vocab"]))
             assert_rows_close(got, rows, 2 * TOL[dtype], f"{dtype} step {step}")
+
+
+def test_command_line_writes_and_generates(tmp_path):
+    """bin/generate: a random-weights folder from a config.json, then greedy tokens from it that equal
+    the plain implementation's on the folder's own tensors."""
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    from mini_gpt_inference_b200.weights import load_file
+
+    root = Path(__file__).resolve().parent.parent
+    raw = config("B", 2.0)
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(raw))
+    folder = tmp_path / "model"
+    made = subprocess.run([sys.executable, str(root / "bin" / "generate"), "--random-weights", "3", "--config", str(cfg_path),
+                           "--write-model", str(folder), "--weights-dtype", "bfloat16"], capture_output=True, text=True)
+    assert made.returncode == 0, made.stderr[-2000:]
+    prompt = tokens_for(raw, 9, 5)
+    run = subprocess.run([sys.executable, str(root / "bin" / "generate"), "--model", str(folder), "--dtype", "float32",
+                          "--prompt-ids", ",".join(map(str, prompt)), "--max-new-tokens", "8", "--temperature", "0"],
+                         capture_output=True, text=True)
+    assert run.returncode == 0, run.stderr[-2000:]
+    out = json.loads(run.stdout.strip().splitlines()[-1])
+    assert out["token_ids"] == plain_greedy(raw, load_file(folder / "model.safetensors"), prompt, 8)
