@@ -94,19 +94,26 @@ class CacheManager:
         self.requests: dict[str, RequestCache] = {}
         self._serial = 0                      # admissions so far
         self._none_needed = (0,) * len(self.groups)
-        self._any_window = any(g.spec.window is not None for g in self.groups)
+        self._any_window = any(self._reach(g.spec) is not None for g in self.groups)
 
     # ---- sizes -------------------------------------------------------------------
+    @staticmethod
+    def _reach(spec: PagedKVSpec) -> int | None:
+        """The most positions back that a query of these layers reads (its own included): the
+        window, or the block of a block mask; None if it reads everything."""
+        bounds = [b for b in (spec.window, spec.block) if b is not None]
+        return min(bounds) if bounds else None
+
     def _geometry(self, spec: PagedKVSpec) -> tuple[int, int]:
         pt = spec.page_tokens or self.page_tokens
         if spec.num_pages is not None:
             return pt, spec.num_pages
         # the default pool holds num_pages * page_tokens tokens, whatever the group's page size
         pages = max(1, self.num_pages * self.page_tokens // pt)
-        if spec.window is not None and self.window_slack_tokens is not None:
+        if self._reach(spec) is not None and self.window_slack_tokens is not None:
             # pages a request can hold at once: the window, the tokens of one step, and the two
             # pages that the window's and the portion's ends share with their neighbours
-            per_request = (spec.window + self.window_slack_tokens + pt - 1) // pt + 2
+            per_request = (self._reach(spec) + self.window_slack_tokens + pt - 1) // pt + 2
             pages = min(pages, self.max_requests * per_request)
         return pt, pages
 
@@ -124,18 +131,20 @@ class CacheManager:
         with a window counts the pages it holds at once, see ``_geometry``)."""
         for group in self.groups:
             need = group.pages_for(num_tokens)
-            if group.spec.window is not None:
+            if self._reach(group.spec) is not None:
                 slack = self.window_slack_tokens if self.window_slack_tokens is not None else num_tokens
-                need = min(need, (group.spec.window + slack + group.page_tokens - 1) // group.page_tokens + 2)
+                need = min(need, (self._reach(group.spec) + slack + group.page_tokens - 1) // group.page_tokens + 2)
             if need > group.num_pages:
                 return False
         return True
 
     def _first_live_page(self, group: CacheGroup, length: int) -> int:
         """Index of the first page that a query at position >= length may still read."""
-        if group.spec.window is None:
-            return 0
-        first_key = max(0, length - group.spec.window + 1)
+        first_key = 0
+        if group.spec.window is not None:
+            first_key = max(0, length - group.spec.window + 1)
+        if group.spec.block is not None:
+            first_key = max(first_key, length // group.spec.block * group.spec.block)
         return first_key // group.page_tokens
 
     def _missing(self, req: RequestCache, new_length: int) -> list[int]:

@@ -26,6 +26,9 @@ class PagedKVSpec:
     num_pages: int | None = None
     # Size of a value head where it differs from a key head's (None: ``head_dim``).
     v_head_dim: int | None = None
+    # Queries read only the keys of their own block of this many positions (blocks counted from
+    # position 0): the pages of blocks that are over can be given back (None: no such mask).
+    block: int | None = None
 
     @property
     def value_dim(self) -> int:
@@ -36,6 +39,8 @@ class PagedKVSpec:
             raise ValueError("n_kv_head, head_dim and v_head_dim must be positive")
         if self.window is not None and self.window <= 0:
             raise ValueError("window must be positive when given")
+        if self.block is not None and self.block <= 0:
+            raise ValueError("block must be positive when given")
         if self.page_tokens is not None and self.page_tokens <= 0:
             raise ValueError("page_tokens must be positive when given")
         if self.num_pages is not None and self.num_pages <= 0:

@@ -18,6 +18,9 @@ Interfaces (what a new part must provide):
                     ``forward(ctx, cache, y, residual32)``  adds its output to residual32 in place
                     and returns None, or returns another tensor that holds the sum
 * FeedForward:      ``forward(ctx, y, residual32)``         the same
+* StreamEntry:      ``forward(ctx, x32, embedded32, index) -> x32``  a transformation of the whole residual
+                    stream between layers (the re-entry of a loop over layers), given the embedding's output
+                    and the number of the pass that begins; it returns a tensor of its own (never ``embedded32``)
 * Block arrangement: a function ``run(ctx, layer, cache, residual32)`` that wires the layer's
                     named parts and returns the tensor that holds the stream (None: in place).
 """
@@ -99,6 +102,11 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class StreamEntry(Part):
+    def forward(self, ctx, x32, embedded32, index: int):
+        raise NotImplementedError
+
+
 class Registry:
     def __init__(self, role: str) -> None:
         self.role = role
@@ -136,6 +144,7 @@ FEED_FORWARDS = Registry("feed-forward")
 ARRANGEMENTS = Registry("block arrangement")
 EMBEDDINGS = Registry("embedding")
 HEADS = Registry("output head")
+STREAM_ENTRIES = Registry("stream entry")
 
 register_norm = NORMS.register
 register_position_encoding = POSITION_ENCODINGS.register
@@ -144,3 +153,4 @@ register_feed_forward = FEED_FORWARDS.register
 register_arrangement = ARRANGEMENTS.register
 register_embedding = EMBEDDINGS.register
 register_head = HEADS.register
+register_stream_entry = STREAM_ENTRIES.register

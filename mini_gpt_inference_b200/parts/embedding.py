@@ -7,10 +7,17 @@ the output head that shares its matrix.
 ``x = scale * tok_emb[id] + ...`` and ``logits = scale * (y @ tok_emb^T)``; the head uses the
 table as stored, without the embedding's scale.  ``tensor_name`` names the table in the
 checkpoint where it is not ``<prefix>weight``.
+
+``hashed_pair_embedding`` adds a row of a second table chosen by the token and the token before
+it: row ``(previous * mul_prev + token * mul_cur) mod buckets``, and the table's last row
+(number ``buckets``) for a sequence's first token.  The token before a step's first token is part
+of the request's state: the embedding keeps it in a slot of the state pool.  ``linear_head`` is
+an output projection with a matrix of its own.
 """
 
 from __future__ import annotations
 
+from ..cache.spec import FixedStateSpec
 from .base import Part, register_embedding, register_head
 from .spec import TensorSpec
 
@@ -84,3 +91,65 @@ class TiedHead(Part):
 
     def _scale_arg(self) -> dict:
         return {} if self.scale == 1.0 else {"scale": self.scale}
+
+
+@register_embedding("hashed_pair_embedding")
+class HashedPairEmbedding(Part):
+    """``x = tok[id] + pair[row(previous id, id)] + pos[p]``; see the module's description."""
+
+    graph_safe = True      # launches kernels only; the token before a step's first one is read on the device
+    takes_token_source = True
+
+    def __init__(self, prefix: str, vocab_size: int, width: int, buckets: int, mul_prev: int, mul_cur: int,
+                 tensor_name: str | None = None, pair_name: str | None = None) -> None:
+        super().__init__(prefix)
+        self.vocab_size, self.width = vocab_size, width
+        self.buckets, self.mul_prev, self.mul_cur = int(buckets), int(mul_prev), int(mul_cur)
+        self.tensor_name = tensor_name if tensor_name is not None else self.prefix + "weight"
+        self.pair_name = pair_name if pair_name is not None else self.prefix + "pair.weight"
+        self.weight = self.pair = None
+
+    def tensor_specs(self):
+        return {self.tensor_name: TensorSpec((self.vocab_size, self.width), "matrix", "unit_normal"),
+                self.pair_name: TensorSpec((self.buckets + 1, self.width), "matrix", "unit_normal")}
+
+    def bind(self, tensors) -> None:
+        self.weight, self.pair = tensors.get(self.tensor_name), tensors.get(self.pair_name)
+
+    def cache_spec(self):
+        return FixedStateSpec((1,), "int32")        # the last token the request brought
+
+    def forward(self, ctx, position, cache):
+        table = position.table() if position is not None else None
+        return ctx.ops.embed_pairs(ctx, self.weight, self.pair, table, self.buckets, self.mul_prev, self.mul_cur,
+                                   cache.state, source=getattr(ctx, "token_source", None),
+                                   previous=getattr(ctx, "fed_ids", None))
+
+
+@register_head("linear_head")
+class LinearHead(Part):
+    """``logits = W y`` with a matrix of the head's own (no bias), 32-bit out."""
+
+    graph_safe = True
+    accepts_deferred_norm = True
+
+    def __init__(self, prefix: str, vocab_size: int, width: int, tensor_name: str | None = None,
+                 embedding=None) -> None:
+        super().__init__(prefix)
+        self.vocab_size, self.width = vocab_size, width
+        self.tensor_name = tensor_name if tensor_name is not None else self.prefix + "weight"
+        self.weight = None
+
+    def tensor_specs(self):
+        return {self.tensor_name: TensorSpec((self.vocab_size, self.width), "matrix", "fan_in")}
+
+    def bind(self, tensors) -> None:
+        self.weight = tensors.get(self.tensor_name)
+
+    def forward(self, ctx, y):
+        greedy_out = getattr(ctx, "greedy_out", None)
+        if greedy_out is not None:
+            logits, ctx.greedy_taken = ctx.ops.logits(y, self.weight, greedy_out,
+                                                      getattr(ctx, "greedy_vocab_limit", None))
+            return logits
+        return ctx.ops.logits(y, self.weight)

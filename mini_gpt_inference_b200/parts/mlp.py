@@ -64,3 +64,42 @@ class DenseMLP(FeedForward):
         h = ctx.ops.linear(y, self.fc_weight, self.fc_bias, self.activation, ctx.act_dtype)
         ctx.ops.linear_residual(h, self.proj_weight, self.proj_bias, residual32)
         return None
+
+
+@register_feed_forward("gated_mlp")
+class GatedMLP(FeedForward):
+    """``down(act(gate(y)) * up(y))`` added into the residual stream, without biases.  ``activation``:
+    ``gelu_tanh`` or ``silu``, evaluated in 32-bit.  The gate's and the up matrix are joined when bound, so
+    a step runs one projection, the gated product and the second projection."""
+
+    graph_safe = True
+    accepts_deferred_norm = True
+
+    def __init__(self, prefix: str, width: int, inner: int, activation: str = "gelu_tanh",
+                 gate_name: str = "gate", up_name: str = "up", down_name: str = "down") -> None:
+        super().__init__(prefix)
+        if activation not in ("gelu_tanh", "silu"):
+            raise ValueError(f"activation {activation!r} is not a gated unit's; known: gelu_tanh, silu")
+        self.width, self.inner, self.activation = width, inner, activation
+        p = self.prefix
+        self._names = {"gate": p + gate_name, "up": p + up_name, "down": p + down_name}
+        self.in_weight = self.down_weight = None
+
+    def tensor_specs(self):
+        n = self._names
+        return {n["gate"]: TensorSpec((self.inner, self.width), "matrix", "fan_in"),
+                n["up"]: TensorSpec((self.inner, self.width), "matrix", "fan_in"),
+                n["down"]: TensorSpec((self.width, self.inner), "matrix", "fan_in_residual")}
+
+    def bind(self, tensors) -> None:
+        import torch
+
+        gate, up = tensors.get(self._names["gate"]), tensors.get(self._names["up"])
+        self.in_weight = torch.cat([gate, up], dim=0).contiguous() if gate is not None and up is not None else None
+        self.down_weight = tensors.get(self._names["down"])
+
+    def forward(self, ctx, y, residual32):
+        ops = ctx.ops
+        hidden = ops.glu(ops.linear(y, self.in_weight, None, "none", ctx.act_dtype), activation=self.activation)
+        ops.linear_residual(hidden, self.down_weight, None, residual32)
+        return None

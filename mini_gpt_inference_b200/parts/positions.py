@@ -15,14 +15,18 @@ from .spec import TensorSpec
 class LearnedAbsolutePositions(PositionEncoding):
     graph_safe = True      # launches kernels only; nothing is decided on the host per step
 
-    def __init__(self, prefix: str, n_positions: int, width: int) -> None:
+    def __init__(self, prefix: str, n_positions: int, width: int, tensor_name: str | None = None) -> None:
         super().__init__(prefix)
         self.n_positions, self.width = n_positions, width
         self.max_positions = n_positions
+        self.tensor_name = tensor_name if tensor_name is not None else self.prefix + "weight"
         self.weight = None
 
     def tensor_specs(self):
-        return {self.prefix + "weight": TensorSpec((self.n_positions, self.width), "matrix")}
+        return {self.tensor_name: TensorSpec((self.n_positions, self.width), "matrix")}
+
+    def bind(self, tensors) -> None:
+        self.weight = tensors.get(self.tensor_name)
 
     def table(self):
         return self.weight

@@ -71,7 +71,7 @@ def check_and_bind(tensors: Mapping[str, torch.Tensor],
                 missing.append(name)
             continue
         t = tensors[name]
-        if tuple(t.shape) != tuple(spec.shape):
+        if not spec.fits(t.shape):
             wrong_shape.append(f"{name}: checkpoint {tuple(t.shape)}, model {tuple(spec.shape)}")
             continue
         if spec.optional_alias_of is not None:

@@ -32,9 +32,9 @@ def random_tensors(model: DecoderModel, seed: int, dtype: torch.dtype = torch.fl
         if spec.optional_alias_of is not None or spec.optional:
             continue
         if spec.role == "table":
-            out[name] = torch.randint(0, 2**15, spec.shape, generator=gen, dtype=torch.int32)
+            out[name] = torch.randint(0, 2**15, spec.init_shape, generator=gen, dtype=torch.int32)
             continue
-        noise = torch.randn(spec.shape, generator=gen, dtype=torch.float32)
+        noise = torch.randn(spec.init_shape, generator=gen, dtype=torch.float32)
         if spec.init == "residual_proj":
             t = noise * (0.02 / math.sqrt(2 * n_layer))
         elif spec.init == "norm_gain":
@@ -43,6 +43,12 @@ def random_tensors(model: DecoderModel, seed: int, dtype: torch.dtype = torch.fl
             t = 0.1 * noise
         elif spec.init == "unit_interval":
             t = torch.sigmoid(noise)
+        elif spec.init == "fan_in":                  # unit-variance outputs for unit-variance inputs
+            t = noise / math.sqrt(spec.init_shape[-1])
+        elif spec.init == "fan_in_residual":
+            t = noise / math.sqrt(spec.init_shape[-1] * 2 * n_layer)
+        elif spec.init == "unit_normal":
+            t = noise
         else:  # "normal", "bias"
             t = 0.02 * noise
         out[name] = t.to(dtype)
