@@ -7,6 +7,11 @@
 // accumulate in 32-bit; keys are visited in blocks of 32 starting at lo, so the result of a
 // (token, head) pair is the same in whichever step and batch it is computed.
 //
+// Two further masks and biases, both parameters: `block` > 0 lets a query see only the keys of its own
+// block of that many positions (lo is raised to the block's first position; blocks are counted from
+// position 0 of the sequence); `slopes` (one number per head) takes slope_h * (p - j) off the score
+// of key j.
+//
 // Any head_dim up to 256 and any number of heads and kv heads (n_head a multiple of
 // n_kv_head) are accepted.  Entries of the block table are read only for positions lo..p, so
 // stale or missing pages elsewhere never matter.
@@ -29,7 +34,7 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, int q_stride, const T*
                                T* __restrict__ out, int n_tokens, int n_head, int n_kv_head, int head_dim, int v_dim,
                                const T* __restrict__ gate, int gate_stride,
                                int page_tokens, int max_pages, int window, float scale, int num_pages,
-                               int n_requests) {
+                               int n_requests, const float* __restrict__ slopes, int block) {
     extern __shared__ float q_smem[];                     // [WARPS][head_dim]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int token = blockIdx.x;
@@ -45,7 +50,9 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, int q_stride, const T*
     // (guarded builds: a position beyond the block table, a request beyond its rows or a page beyond
     // the pool is recorded, and position 0, request 0 or page 0 is read in its place)
     if (!MG_GUARDED(attention_generic, MG_GUARD_POSITION, p, (long long)max_pages * page_tokens)) p = 0;
-    const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    if (block > 0) lo = max(lo, p / block * block);
+    const float slope = slopes ? slopes[head] : 0.f;
     int request = token_request[token];
     if (!MG_GUARDED(attention_generic, MG_GUARD_REQUEST, request, n_requests)) request = 0;
     const int* table = block_table + (size_t)request * max_pages;
@@ -72,7 +79,7 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, int q_stride, const T*
             const T* kr = k_pages + (size_t)row * head_dim;
             float dot = 0.f;
             for (int d = 0; d < head_dim; ++d) dot = fmaf(q[d], to_float(kr[d]), dot);
-            s = dot;
+            s = slopes ? dot - slope * (float)(p - j) : dot;
         }
         const float new_max = fmaxf(run_max, warp_max(s));
         const float prob = valid ? expf(s - new_max) : 0.f;
@@ -114,7 +121,8 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, int q_stride, const T*
 // [page, kv head, page_tokens, head_dim], value pages [page, kv head, page_tokens, v_dim] (keys and
 // values may differ in size); block_table: [n_requests, max_pages]; out: [n_tokens, n_head * v_dim].
 // gate (may be null): rows of `gate_stride` elements whose first n_head * v_dim hold gate values; the
-// output is multiplied by their logistic function.  window <= 0: none.
+// output is multiplied by their logistic function.  window <= 0: none.  slopes: [n_head] 32-bit or null;
+// key_block <= 0: no block mask.
 // num_pages: pages of the pool (with n_requests, what guarded builds hold the indices against).
 MG_API int mg_paged_attention_general(const void* q, int q_stride, const void* k_pages, const void* v_pages,
                                       const int* block_table, const int* token_request,
@@ -122,9 +130,9 @@ MG_API int mg_paged_attention_general(const void* q, int q_stride, const void* k
                                       int n_kv_head, int head_dim, int v_dim, const void* gate, int gate_stride,
                                       int page_tokens, int max_pages,
                                       int window, float scale, int num_pages, int n_requests, int is_bf16,
-                                      void* stream) {
+                                      const float* slopes, int key_block, void* stream) {
     if (n_tokens == 0) return MG_OK;
-    MG_REQUIRE(n_tokens > 0 && n_head > 0 && n_kv_head > 0 && page_tokens > 0 && max_pages > 0,
+    MG_REQUIRE(n_tokens > 0 && n_head > 0 && n_kv_head > 0 && page_tokens > 0 && max_pages > 0 && key_block >= 0,
                "attention: bad sizes");
     MG_REQUIRE(n_head % n_kv_head == 0, "attention: n_head %d is not a multiple of n_kv_head %d", n_head, n_kv_head);
     MG_REQUIRE(head_dim > 0 && head_dim <= 32 * MAX_DPL, "attention: head_dim %d is outside 1..%d", head_dim, 32 * MAX_DPL);
@@ -139,12 +147,12 @@ MG_API int mg_paged_attention_general(const void* q, int q_stride, const void* k
         paged_attention_generic_kernel<bf16><<<grid, block, smem, s>>>(
             (const bf16*)q, q_stride, (const bf16*)k_pages, (const bf16*)v_pages, block_table, token_request, positions,
             (bf16*)out, n_tokens, n_head, n_kv_head, head_dim, v_dim, (const bf16*)gate, gate_stride, page_tokens,
-            max_pages, window, scale, num_pages, n_requests);
+            max_pages, window, scale, num_pages, n_requests, slopes, key_block);
     else
         paged_attention_generic_kernel<float><<<grid, block, smem, s>>>(
             (const float*)q, q_stride, (const float*)k_pages, (const float*)v_pages, block_table, token_request, positions,
             (float*)out, n_tokens, n_head, n_kv_head, head_dim, v_dim, (const float*)gate, gate_stride, page_tokens,
-            max_pages, window, scale, num_pages, n_requests);
+            max_pages, window, scale, num_pages, n_requests, slopes, key_block);
     MG_CHECK_LAUNCH("paged_attention_generic");
     return MG_OK;
 }
@@ -160,5 +168,5 @@ MG_API int mg_paged_attention_generic(const void* qkv, const void* k_pages, cons
     return mg_paged_attention_general(qkv, (n_head + 2 * n_kv_head) * head_dim, k_pages, v_pages, block_table,
                                       token_request, positions, out, n_tokens, n_head, n_kv_head, head_dim, head_dim,
                                       nullptr, 0, page_tokens, max_pages, window, scale, num_pages, n_requests, is_bf16,
-                                      stream);
+                                      nullptr, 0, stream);
 }

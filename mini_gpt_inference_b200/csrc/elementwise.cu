@@ -58,6 +58,170 @@ MG_API int mg_embed(const int* ids, const int* pos, const void* tok, const void*
     return MG_OK;
 }
 
+// ---- embedding + hashed token-pair embedding + learned position add ------------------------------------
+// x[n, :] = tok[id[n], :] + pair[row, :] + pos_emb[pos[n], :], row = (id of the token before * mul_prev +
+// id[n] * mul_cur) mod buckets, or `buckets` (the table's last row) for a request's very first token.  The
+// token before a step's first token of a request is read from the request's state slot; the block of
+// that first token also leaves the request's last token of this step there (it is the only block that
+// touches the slot, and it reads before it writes).
+template <typename TW>
+__global__ void embed_pairs_kernel(const int* __restrict__ ids, const int* __restrict__ pos,
+                                   const int* __restrict__ token_request, const int* __restrict__ req_q_start,
+                                   const int* __restrict__ req_q_len, const int* __restrict__ req_ctx_before,
+                                   const int* __restrict__ req_state_slot, const TW* __restrict__ tok,
+                                   const TW* __restrict__ pair, const TW* __restrict__ ptab, float* __restrict__ out,
+                                   int* __restrict__ state, int state_stride, int width, const int* __restrict__ source,
+                                   const int* __restrict__ previous, int vocab, int n_positions, int n_previous,
+                                   int buckets, int mul_prev, int mul_cur, int n_requests, int n_slots, int n_tokens) {
+    __shared__ int row_s, id_s;
+    const int n = blockIdx.x;
+    float* orow = out + (size_t)n * width;
+    int p = pos[n];
+    if (p < 0) {
+        for (int c = threadIdx.x; c < width; c += blockDim.x) orow[c] = 0.f;
+        return;
+    }
+    if (threadIdx.x == 0) {
+        auto fetch = [&](int i) {
+            int id = ids[i];
+            if (source != nullptr) {
+                const int src = source[i];
+                if (src >= 0 && MG_GUARDED(elementwise, MG_GUARD_SOURCE, src, n_previous)) id = previous[src];
+            }
+            if (!MG_GUARDED(elementwise, MG_GUARD_TOKEN, id, vocab)) id = 0;
+            return id;
+        };
+        const int id = fetch(n);
+        int r = token_request[n];
+        if (!MG_GUARDED(elementwise, MG_GUARD_REQUEST, r, n_requests)) r = 0;
+        const int start = req_q_start[r];
+        int slot = req_state_slot[r];
+        if (!MG_GUARDED(elementwise, MG_GUARD_ROW, slot, n_slots)) slot = 0;
+        int before = -1;
+        if (n > start) before = fetch(n - 1);
+        else if (req_ctx_before[r] > 0) before = state[(size_t)slot * state_stride];
+        if (n == start) {
+            int last = start + req_q_len[r] - 1;
+            if (!MG_GUARDED(elementwise, MG_GUARD_ROW, last, n_tokens)) last = n;
+            state[(size_t)slot * state_stride] = fetch(last);
+        }
+        row_s = before < 0 ? buckets
+                           : (int)(((long long)before * mul_prev + (long long)id * mul_cur) % (long long)buckets);
+        id_s = id;
+    }
+    __syncthreads();
+    if (ptab != nullptr && !MG_GUARDED(elementwise, MG_GUARD_POSITION, p, n_positions)) p = 0;
+    const TW* trow = tok + (size_t)id_s * width;
+    const TW* brow = pair + (size_t)row_s * width;
+    const TW* prow = ptab ? ptab + (size_t)p * width : nullptr;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float v = to_float(trow[c]) + to_float(brow[c]);
+        if (prow) v += to_float(prow[c]);
+        orow[c] = v;
+    }
+}
+
+// state: [n_slots, state_stride] ints, the first of each slot holds the request's last token.
+MG_API int mg_embed_pairs(const int* ids, const int* pos, const int* token_request, const int* req_q_start,
+                          const int* req_q_len, const int* req_ctx_before, const int* req_state_slot, const void* tok,
+                          const void* pair, const void* ptab, float* out, int* state, int state_stride, int n_tokens,
+                          int width, int weights_bf16, const int* source, const int* previous, int vocab,
+                          int n_positions, int n_previous, int buckets, int mul_prev, int mul_cur, int n_requests,
+                          int n_slots, void* stream) {
+    if (n_tokens == 0) return MG_OK;
+    MG_REQUIRE(n_tokens > 0 && width > 0 && vocab > 0 && buckets > 0 && n_requests > 0 && n_slots > 0 && state_stride > 0,
+               "embed_pairs: bad sizes");
+    MG_REQUIRE(mul_prev >= 0 && mul_cur >= 0, "embed_pairs: negative multipliers");
+    MG_REQUIRE(source == nullptr || previous != nullptr, "embed_pairs: token sources without the ids they point to");
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = width >= 256 ? 256 : 128;
+    if (weights_bf16)
+        embed_pairs_kernel<bf16><<<n_tokens, threads, 0, s>>>(
+            ids, pos, token_request, req_q_start, req_q_len, req_ctx_before, req_state_slot, (const bf16*)tok,
+            (const bf16*)pair, (const bf16*)ptab, out, state, state_stride, width, source, previous, vocab, n_positions,
+            n_previous, buckets, mul_prev, mul_cur, n_requests, n_slots, n_tokens);
+    else
+        embed_pairs_kernel<float><<<n_tokens, threads, 0, s>>>(
+            ids, pos, token_request, req_q_start, req_q_len, req_ctx_before, req_state_slot, (const float*)tok,
+            (const float*)pair, (const float*)ptab, out, state, state_stride, width, source, previous, vocab, n_positions,
+            n_previous, buckets, mul_prev, mul_cur, n_requests, n_slots, n_tokens);
+    MG_CHECK_LAUNCH("embed_pairs");
+    return MG_OK;
+}
+
+// ---- RMS norm ---------------------------------------------------------------------------------
+// One warp per row, 32-bit: y = x / sqrt(mean(x^2) + eps) * (offset + w).  A row's result depends on
+// nothing but the row (a lane sums every 32nd group of four values in a fixed order).
+template <typename TOut>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, TOut* __restrict__ y, int rows,
+                               int width, float eps, float offset) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * (blockDim.x >> 5) + warp;
+    pdl_trigger();
+    pdl_wait();                                        // x comes from the kernel in front
+    if (row >= rows) return;
+    const float* xr = x + (size_t)row * width;
+    TOut* yr = y + (size_t)row * width;
+    if (width % 4 == 0 && (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) & 15) == 0) {
+        const float4* x4 = reinterpret_cast<const float4*>(xr);
+        const float4* w4 = reinterpret_cast<const float4*>(w);
+        const int n4 = width / 4;
+        float sq = 0.f;
+        for (int c = lane; c < n4; c += 32) {
+            const float4 v = x4[c];
+            sq += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
+        }
+        const float r = 1.0f / sqrtf(warp_sum(sq) / (float)width + eps);
+        for (int c = lane; c < n4; c += 32) {
+            const float4 v = x4[c], g = w4[c];
+            store4(yr + 4 * c, v.x * r * (offset + g.x), v.y * r * (offset + g.y), v.z * r * (offset + g.z),
+                   v.w * r * (offset + g.w));
+        }
+        return;
+    }
+    float sq = 0.f;
+    for (int c = lane; c < width; c += 32) sq = fmaf(xr[c], xr[c], sq);
+    const float r = 1.0f / sqrtf(warp_sum(sq) / (float)width + eps);
+    for (int c = lane; c < width; c += 32) yr[c] = from_float<TOut>(xr[c] * r * (offset + w[c]));
+}
+
+MG_API int mg_rmsnorm(const float* x, const float* w, void* y, int rows, int width, float eps, float offset, int out_bf16,
+                      void* stream) {
+    if (rows == 0) return MG_OK;
+    MG_REQUIRE(rows > 0 && width > 0, "rmsnorm: bad sizes");
+    cudaStream_t s = (cudaStream_t)stream;
+    const int warps = 4;
+    dim3 grid(ceil_div(rows, warps)), block(32 * warps);
+    const cudaError_t le = out_bf16 ? mg_launch(rmsnorm_kernel<bf16>, grid, block, 0, s, true, x, w, (bf16*)y, rows, width, eps, offset)
+                                    : mg_launch(rmsnorm_kernel<float>, grid, block, 0, s, true, x, w, (float*)y, rows, width, eps, offset);
+    if (le != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "rmsnorm: %s", cudaGetErrorString(le));
+    return MG_OK;
+}
+
+// ---- two 32-bit row sets side by side, in the compute type: out[n] = [a[n] ; b[n]] ------------------------
+template <typename TOut>
+__global__ void concat_cast_kernel(const float* __restrict__ a, const float* __restrict__ b, TOut* __restrict__ out,
+                                   int width) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t n = blockIdx.x;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        out[n * 2 * width + c] = from_float<TOut>(a[n * width + c]);
+        out[n * 2 * width + width + c] = from_float<TOut>(b[n * width + c]);
+    }
+}
+
+MG_API int mg_concat_cast(const float* a, const float* b, void* out, int rows, int width, int out_bf16, void* stream) {
+    if (rows == 0) return MG_OK;
+    MG_REQUIRE(rows > 0 && width > 0, "concat: bad sizes");
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid(rows), block(width >= 256 ? 256 : 128);
+    const cudaError_t le = out_bf16 ? mg_launch(concat_cast_kernel<bf16>, grid, block, 0, s, true, a, b, (bf16*)out, width)
+                                    : mg_launch(concat_cast_kernel<float>, grid, block, 0, s, true, a, b, (float*)out, width);
+    if (le != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "concat: %s", cudaGetErrorString(le));
+    return MG_OK;
+}
+
 // ---- LayerNorm -----------------------------------------------------------------------------
 // One warp per row.  Mean, then the biased variance of the centred values, then the affine
 // map; all in 32-bit.  y = (x - mean) * rsqrt(var + eps) * gain (+ shift).

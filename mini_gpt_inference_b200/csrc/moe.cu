@@ -104,6 +104,122 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w_router, co
     for (int k = lane; k < top; k += 32) weights[(size_t)token * top + k] *= inv;
 }
 
+// ---- router with scores per expert, a correction for the choice, and groups --------------------------
+// scoring 1: s = sigmoid(z), weights = scale * s of the chosen experts (not renormalised);
+// scoring 0: s = z, weights = scale * softmax over the chosen z.
+// Choice scores c = s + correction (correction may be null).  With n_groups > 0 the experts form n_groups equal
+// groups of neighbours; a group's score is the sum of its two largest c (of its one c, if it has one expert),
+// and only experts of the `keep` best groups can be chosen.  Ties go to the lower index.
+__device__ __forceinline__ void warp_argmax(float& best, int& best_i) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        if (ov > best || (ov == best && oi < best_i)) best = ov, best_i = oi;
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(32 * ROUTE_WARPS)
+moe_route_scored_kernel(const T* __restrict__ h, const float* __restrict__ w_router, const float* __restrict__ w_gate,
+                        const float* __restrict__ correction, const int* __restrict__ positions, int* __restrict__ ids,
+                        float* __restrict__ weights, float* __restrict__ gate, int n_tokens, int width, int n_experts,
+                        int top, int scoring, int n_groups, int keep, float scale) {
+    extern __shared__ float route_smem[];                  // s [n_experts], c [n_experts], group scores [n_groups]
+    float* s_of = route_smem;
+    float* c_of = route_smem + n_experts;
+    float* g_of = c_of + n_experts;
+    pdl_trigger();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int token = blockIdx.x;
+    if (positions != nullptr && positions[token] < 0) {
+        for (int k = threadIdx.x; k < top; k += blockDim.x) {
+            ids[(size_t)token * top + k] = -1;
+            weights[(size_t)token * top + k] = 0.f;
+        }
+        if (gate != nullptr && threadIdx.x == 0) gate[token] = 0.f;
+        return;
+    }
+    const T* row = h + (size_t)token * width;
+    const bool vec = width % 4 == 0 && ((uintptr_t)w_router % 16 == 0) && (w_gate == nullptr || (uintptr_t)w_gate % 16 == 0);
+    const int rows = n_experts + (gate != nullptr ? 1 : 0);
+    for (int e = warp; e < rows; e += ROUTE_WARPS) {
+        const float dot = route_dot(row, e < n_experts ? w_router + (size_t)e * width : w_gate, width, lane, vec);
+        if (lane == 0) {
+            if (e < n_experts) {
+                const float s = scoring ? 1.0f / (1.0f + expf(-dot)) : dot;
+                s_of[e] = s;
+                c_of[e] = correction ? s + correction[e] : s;
+            } else {
+                gate[token] = 1.0f / (1.0f + expf(-dot));
+            }
+        }
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    if (n_groups > 0) {
+        const int per = n_experts / n_groups;
+        for (int g = lane; g < n_groups; g += 32) {
+            float a = -INFINITY, b = -INFINITY;            // the two largest of the group
+            for (int e = g * per; e < (g + 1) * per; ++e) {
+                const float v = c_of[e];
+                if (v > a) b = a, a = v;
+                else if (v > b) b = v;
+            }
+            g_of[g] = per > 1 ? a + b : a;
+        }
+        __syncwarp();
+        // the `keep` best groups are marked by a score of +inf, then all others lose their experts
+        for (int k = 0; k < keep; ++k) {
+            float best = -INFINITY;
+            int best_g = 0x7fffffff;
+            for (int g = lane; g < n_groups; g += 32) {
+                const float v = g_of[g];
+                if (v != INFINITY && (v > best || (v == best && g < best_g))) best = v, best_g = g;
+            }
+            warp_argmax(best, best_g);
+            if (best_g >= n_groups) {                      // scores that are not numbers: the first group not yet kept
+                best_g = 0;
+                while (best_g < n_groups - 1 && g_of[best_g] == INFINITY) ++best_g;
+            }
+            if (lane == 0) g_of[best_g] = INFINITY;
+            __syncwarp();
+        }
+        for (int e = lane; e < n_experts; e += 32)
+            if (g_of[e / per] != INFINITY) c_of[e] = -INFINITY;
+        __syncwarp();
+    }
+    float first = 0.f, sum = 0.f;
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int best_e = 0x7fffffff;
+        for (int e = lane; e < n_experts; e += 32) {
+            const float v = c_of[e];
+            if (v > best || (v == best && e < best_e)) best = v, best_e = e;
+        }
+        warp_argmax(best, best_e);
+        if (best_e >= n_experts) best_e = k;               // scores that are not numbers: still a valid choice
+        const float s = s_of[best_e];
+        float w = s * scale;
+        if (!scoring) {
+            if (k == 0) first = s;
+            w = expf(s - first);
+            sum += w;
+        }
+        if (lane == 0) {
+            ids[(size_t)token * top + k] = best_e;
+            weights[(size_t)token * top + k] = w;
+            c_of[best_e] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    if (!scoring) {
+        const float inv = scale / sum;
+        for (int k = lane; k < top; k += 32) weights[(size_t)token * top + k] *= inv;
+    }
+}
+
 // ---- grouping -----------------------------------------------------------------------------------
 // Block e finds the entries that chose expert e: offsets[e] = entries that chose a lower expert,
 // and each of its entries gets slot offsets[e] + (its rank among them, in entry order).
@@ -167,13 +283,26 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
 
 __device__ __forceinline__ float silu(float z) { return z / (1.0f + expf(-z)); }
 
+// The gated product of a unit's two hidden features g (gate) and u (up), by `act`:
+//   0: silu(g) * u        1: g' * sigmoid(1.702 g') * (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit)
+//   2: gelu_tanh(g) * u
+__device__ __forceinline__ float gated_value(int act, float limit, float g, float u) {
+    if (act == 1) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+    }
+    if (act == 2) return gelu_tanh(g) * u;
+    return silu(g) * u;
+}
+
 // GLU = true:  out[slot, n] = silu(a . w[e][n]) * (a . w[e][inner + n]),  a = x[token of slot]   (T out)
 // GLU = false: out[slot, n] = scale[entry of slot] * (a . w[e][n]),       a = x[slot]            (32-bit out)
 template <typename T, bool GLU>
 __global__ void __launch_bounds__(256)
 moe_gemm_kernel(const T* __restrict__ x, int ldx, const T* __restrict__ w, long long w_expert_stride,
                 const int* __restrict__ offsets, const int* __restrict__ slot_entry, int top,
-                const float* __restrict__ scale, void* __restrict__ out, int N, int K, int x_rows) {
+                const float* __restrict__ scale, void* __restrict__ out, int N, int K, int x_rows, int act, float limit) {
     __shared__ float as[BK][BM + 4];
     __shared__ float ws[BK][BN + 4];
     __shared__ float us[GLU ? BK : 1][BN + 4];
@@ -249,7 +378,7 @@ moe_gemm_kernel(const T* __restrict__ x, int ldx, const T* __restrict__ w, long 
             const int n = n0 + tc * TN + j;
             if (n >= N) continue;
             if constexpr (GLU)
-                reinterpret_cast<T*>(out)[slot * N + n] = from_float<T>(silu(acc[i][j]) * acc_u[i][j]);
+                reinterpret_cast<T*>(out)[slot * N + n] = from_float<T>(gated_value(act, limit, acc[i][j], acc_u[i][j]));
             else
                 reinterpret_cast<float*>(out)[slot * N + n] = acc[i][j] * sc;
         }
@@ -290,7 +419,7 @@ template <bool GLU, int MB, int NS>
 __global__ void __launch_bounds__(128)
 moe_gemm_mma_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ w, long long w_expert_stride,
                     const int* __restrict__ offsets, const int* __restrict__ slot_entry, int top,
-                    const float* __restrict__ scale, void* __restrict__ out, int N, int K, int x_rows) {
+                    const float* __restrict__ scale, void* __restrict__ out, int N, int K, int x_rows, int act, float limit) {
     extern __shared__ __align__(16) uint8_t moe_smem[];
     bf16* as = reinterpret_cast<bf16*>(moe_smem);          // [NS][MT * MLD]
     bf16* bs = as + NS * MT * MLD;                         // [NS][MB * MLD]
@@ -406,8 +535,8 @@ moe_gemm_mma_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int n = n0 + wc * 32 + j * 8 + 2 * (lane & 3);
-                    const float v0 = silu(acc[i][j][2 * half]) * acc[i][j + 4][2 * half];
-                    const float v1 = silu(acc[i][j][2 * half + 1]) * acc[i][j + 4][2 * half + 1];
+                    const float v0 = gated_value(act, limit, acc[i][j][2 * half], acc[i][j + 4][2 * half]);
+                    const float v1 = gated_value(act, limit, acc[i][j][2 * half + 1], acc[i][j + 4][2 * half + 1]);
                     bf16* o = reinterpret_cast<bf16*>(out) + slot * N + n;
                     if (n + 1 < N && (N & 1) == 0) *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(v0, v1);
                     else {
@@ -447,14 +576,14 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
 // ---- out[n, j] = silu(gu[n, j]) * gu[n, inner + j] (* scale[n]) -----------------------------------
 template <typename T>
 __global__ void glu_kernel(const T* __restrict__ gu, const float* __restrict__ scale, T* __restrict__ out, int rows,
-                           int inner) {
+                           int inner, int act, float limit) {
     pdl_trigger();
     pdl_wait();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (long long)rows * inner) return;
     const int n = (int)(i / inner), j = (int)(i - (long long)n * inner);
     const float g = to_float(gu[(size_t)n * 2 * inner + j]), u = to_float(gu[(size_t)n * 2 * inner + inner + j]);
-    float v = silu(g) * u;
+    float v = gated_value(act, limit, g, u);
     if (scale != nullptr) v *= scale[n];
     out[i] = from_float<T>(v);
 }
@@ -489,6 +618,34 @@ MG_API int mg_moe_route(const void* h, const float* w_router, const float* w_gat
     return MG_OK;
 }
 
+// As mg_moe_route, with scores per expert (scoring 1: sigmoid, 0: the logits with a softmax over the chosen),
+// correction: [n_experts] 32-bit or null, n_groups / keep: the groups (0: none), scale: factor on the weights.
+MG_API int mg_moe_route_scored(const void* h, const float* w_router, const float* w_gate, const float* correction,
+                               const int* positions, int* ids, float* weights, float* gate, int n_tokens, int width,
+                               int n_experts, int top, int scoring, int n_groups, int keep, float scale, int is_bf16,
+                               void* stream) {
+    if (n_tokens == 0) return MG_OK;
+    MG_REQUIRE(n_tokens > 0 && width > 0 && n_experts > 0 && top > 0 && top <= n_experts, "moe route: bad sizes");
+    MG_REQUIRE((w_gate == nullptr) == (gate == nullptr), "moe route: a gate wants its weights and its output");
+    MG_REQUIRE(n_groups >= 0 && (n_groups == 0 || (n_experts % n_groups == 0 && keep > 0 && keep <= n_groups &&
+                                                   keep * (n_experts / n_groups) >= top)),
+               "moe route: %d groups of which %d are kept do not fit %d experts and %d choices", n_groups, keep, n_experts, top);
+    const size_t smem = (size_t)(2 * n_experts + n_groups) * sizeof(float);
+    MG_REQUIRE(smem <= 48 * 1024, "moe route: too many experts (%d)", n_experts);
+    const dim3 grid(n_tokens), block(32 * ROUTE_WARPS);
+    cudaError_t e;
+    if (is_bf16)
+        e = mg_launch(moe_route_scored_kernel<bf16>, grid, block, smem, (cudaStream_t)stream, true, (const bf16*)h, w_router,
+                      w_gate, correction, positions, ids, weights, gate, n_tokens, width, n_experts, top, scoring, n_groups,
+                      keep, scale);
+    else
+        e = mg_launch(moe_route_scored_kernel<float>, grid, block, smem, (cudaStream_t)stream, true, (const float*)h, w_router,
+                      w_gate, correction, positions, ids, weights, gate, n_tokens, width, n_experts, top, scoring, n_groups,
+                      keep, scale);
+    MG_LAUNCHED(e, "moe route (scored)");
+    return MG_OK;
+}
+
 // ids: [n_entries] chosen experts (-1: none); offsets: [n_experts + 1]; slot_entry, entry_slot: [n_entries].
 MG_API int mg_moe_group(const int* ids, int n_entries, int n_experts, int* offsets, int* slot_entry, int* entry_slot,
                         void* stream) {
@@ -500,12 +657,13 @@ MG_API int mg_moe_group(const int* ids, int n_entries, int n_experts, int* offse
     return MG_OK;
 }
 
+// act, limit: the gated product of the first product's two halves (see gated_value).
 // glu = 1: x [x_rows, ldx] gathered by token, w [n_experts, 2 N, K], out [n_entries, N] in the inputs' type.
 // glu = 0: x [n_entries, ldx] by slot, w [n_experts, N, K], scale [n_entries] by entry, out [n_entries, N] 32-bit.
 // max_rows: the most slots one expert can have (the tokens of the step).
 MG_API int mg_moe_gemm(const void* x, int ldx, const void* w, const int* offsets, const int* slot_entry, int top,
                        const float* scale, void* out, int n_experts, int max_rows, int N, int K, int x_rows, int glu,
-                       int is_bf16, void* stream) {
+                       int is_bf16, int act, float limit, void* stream) {
     if (max_rows == 0) return MG_OK;
     MG_REQUIRE(n_experts > 0 && n_experts <= 65535 && max_rows > 0 && N > 0 && K > 0 && ldx >= K && top > 0,
                "moe gemm: bad sizes");
@@ -537,28 +695,28 @@ MG_API int mg_moe_gemm(const void* x, int ldx, const void* w, const int* offsets
         const bf16* wb = (const bf16*)w;
         if (glu && few)
             e = mg_launch(moe_gemm_mma_kernel<true, 64, 4>, tgrid, dim3(128), moe_mma_smem(64, 4), s, true, xb, ldx, wb, stride,
-                          offsets, slot_entry, top, scale, out, N, K, x_rows);
+                          offsets, slot_entry, top, scale, out, N, K, x_rows, act, limit);
         else if (glu)
             e = mg_launch(moe_gemm_mma_kernel<true, 128, 2>, tgrid, dim3(128), moe_mma_smem(128, 2), s, true, xb, ldx, wb, stride,
-                          offsets, slot_entry, top, scale, out, N, K, x_rows);
+                          offsets, slot_entry, top, scale, out, N, K, x_rows, act, limit);
         else if (few)
             e = mg_launch(moe_gemm_mma_kernel<false, 64, 4>, tgrid, dim3(128), moe_mma_smem(64, 4), s, true, xb, ldx, wb, stride,
-                          offsets, slot_entry, top, scale, out, N, K, x_rows);
+                          offsets, slot_entry, top, scale, out, N, K, x_rows, act, limit);
         else
             e = mg_launch(moe_gemm_mma_kernel<false, 128, 2>, tgrid, dim3(128), moe_mma_smem(128, 2), s, true, xb, ldx, wb, stride,
-                          offsets, slot_entry, top, scale, out, N, K, x_rows);
+                          offsets, slot_entry, top, scale, out, N, K, x_rows, act, limit);
     } else if (is_bf16 && glu)
         e = mg_launch(moe_gemm_kernel<bf16, true>, grid, block, 0, s, true, (const bf16*)x, ldx, (const bf16*)w, stride,
-                      offsets, slot_entry, top, scale, out, N, K, x_rows);
+                      offsets, slot_entry, top, scale, out, N, K, x_rows, act, limit);
     else if (is_bf16)
         e = mg_launch(moe_gemm_kernel<bf16, false>, grid, block, 0, s, true, (const bf16*)x, ldx, (const bf16*)w, stride,
-                      offsets, slot_entry, top, scale, out, N, K, x_rows);
+                      offsets, slot_entry, top, scale, out, N, K, x_rows, act, limit);
     else if (glu)
         e = mg_launch(moe_gemm_kernel<float, true>, grid, block, 0, s, true, (const float*)x, ldx, (const float*)w, stride,
-                      offsets, slot_entry, top, scale, out, N, K, x_rows);
+                      offsets, slot_entry, top, scale, out, N, K, x_rows, act, limit);
     else
         e = mg_launch(moe_gemm_kernel<float, false>, grid, block, 0, s, true, (const float*)x, ldx, (const float*)w,
-                      stride, offsets, slot_entry, top, scale, out, N, K, x_rows);
+                      stride, offsets, slot_entry, top, scale, out, N, K, x_rows, act, limit);
     MG_LAUNCHED(e, "moe gemm");
     return MG_OK;
 }
@@ -575,7 +733,8 @@ MG_API int mg_moe_combine(const float* y, const int* entry_slot, int top, float*
 }
 
 // gu: [rows, 2 inner] (gate columns first); scale: [rows] 32-bit or null; out: [rows, inner].
-MG_API int mg_glu(const void* gu, const float* scale, void* out, int rows, int inner, int is_bf16, void* stream) {
+MG_API int mg_glu(const void* gu, const float* scale, void* out, int rows, int inner, int is_bf16, int act, float limit,
+                  void* stream) {
     if (rows == 0) return MG_OK;
     MG_REQUIRE(rows > 0 && inner > 0, "glu: bad sizes");
     const long long n = (long long)rows * inner;
@@ -583,10 +742,10 @@ MG_API int mg_glu(const void* gu, const float* scale, void* out, int rows, int i
     cudaError_t e;
     if (is_bf16)
         e = mg_launch(glu_kernel<bf16>, grid, block, 0, (cudaStream_t)stream, true, (const bf16*)gu, scale, (bf16*)out,
-                      rows, inner);
+                      rows, inner, act, limit);
     else
         e = mg_launch(glu_kernel<float>, grid, block, 0, (cudaStream_t)stream, true, (const float*)gu, scale, (float*)out,
-                      rows, inner);
+                      rows, inner, act, limit);
     MG_LAUNCHED(e, "glu");
     return MG_OK;
 }

@@ -23,16 +23,24 @@ _SIGNATURES = {
     "mg_guards_enabled": [],
     "mg_embed": [_P, _P, _P, _P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _F, _P],
     "mg_scale": [_P, ctypes.c_longlong, _F, _P],
-    "mg_head_prepare": [_P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P],
+    "mg_head_prepare": [_P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P, _P],
     "mg_paged_attention_general": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _I, _I, _I, _F,
-                                   _I, _I, _I, _P],
+                                   _I, _I, _I, _P, _I, _P],
+    "mg_embed_pairs": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I,
+                       _I, _I, _P],
+    "mg_rmsnorm": [_P, _P, _P, _I, _I, _F, _F, _I, _P],
+    "mg_concat_cast": [_P, _P, _P, _I, _I, _I, _P],
+    "mg_matrix_memory_scan": [_P, _I, _I, _I, _I, _P, _I, _P, _P, _P, _P, _P, ctypes.c_longlong, _P, _P, _I, _I, _I, _I,
+                              _I, _F, _I, _I, _I, _P],
+    "mg_head_norm_gate": [_P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _F, _I, _I, _I, _P],
+    "mg_moe_route_scored": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "mg_attention_mma": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F,
                          _I, _I, _I, _I, _I, _I, _P],
     "mg_moe_route": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "mg_moe_group": [_P, _I, _I, _P, _P, _P, _P],
-    "mg_moe_gemm": [_P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+    "mg_moe_gemm": [_P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P],
     "mg_moe_combine": [_P, _P, _I, _P, _I, _I, _I, _P],
-    "mg_glu": [_P, _P, _P, _I, _I, _I, _P],
+    "mg_glu": [_P, _P, _P, _I, _I, _I, _I, _F, _P],
     "mg_layernorm": [_P, _P, _P, _P, _I, _I, _F, _I, _P],
     "mg_gather_rows": [_P, _P, _P, _I, _I, _I, _P],
     "mg_gather_tokens": [_P, _P, _P, _I, _I, _P],
@@ -68,7 +76,7 @@ _SIGNATURES = {
 
 # exported readers of the kernel files' index guards: mg_<name>_index_fault(long long[4])
 GUARDED_FILES = ("elementwise", "linear_skinny", "linear_stream", "linear_wide", "linear_cluster", "linear_tc",
-                 "attention_generic", "attention_split", "attention_prefill", "head_prepare", "moe", "attention_mma")
+                 "attention_generic", "attention_split", "attention_prefill", "head_prepare", "moe", "attention_mma", "matrix_memory")
 for _name in GUARDED_FILES:
     _SIGNATURES[f"mg_{_name}_index_fault"] = [_P]
 GUARD_CODES = {1: "token id", 2: "position", 3: "cache row", 4: "page", 5: "request", 6: "row", 7: "token source"}

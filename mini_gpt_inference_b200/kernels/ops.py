@@ -18,6 +18,7 @@ from .attention_plan import KEY_CHUNK, query_tiles
 from .library import KernelLibraryError, check
 
 EPILOGUES = {"none": 0, "gelu_tanh": 1, "residual": 2, "relu_sq": 3}
+GATED_ACTIVATIONS = {"silu": 0, "clamped_swish": 1, "gelu_tanh": 2}     # the gated product of a unit's two halves
 SKINNY_ROWS = 16         # most tokens the small-batch projection kernel takes
 CLUSTER_ROWS = 128       # most tokens the mid-batch (K split over a cluster) projection kernel takes
 CLUSTER_WIDE_MAX_BYTES = 3 << 20   # ... and the largest matrix it is given for more than 64 tokens
@@ -250,6 +251,114 @@ class CudaOps:
         out = torch.empty((rows, width), dtype=out_dtype, device=self.device)
         self._run(self.lib.mg_layernorm(_ptr(x32), _ptr(gain), _ptr(shift), _ptr(out), rows, width,
                                     float(eps), self._is_bf16(out), self._stream()), "layernorm")
+        return out
+
+    def rmsnorm(self, x32, weight, eps, offset, out_dtype):
+        """``x / sqrt(mean(x^2) + eps) * (offset + weight)``, statistics in 32-bit."""
+        self._want(x32, torch.float32, "rmsnorm input", 2)
+        self._want(weight, torch.float32, "rmsnorm weight", 1)
+        rows, width = x32.shape
+        if weight.numel() != width:
+            raise KernelLibraryError("rmsnorm: the weight does not match the width")
+        out = torch.empty((rows, width), dtype=out_dtype, device=self.device)
+        self._run(self.lib.mg_rmsnorm(_ptr(x32), _ptr(weight), _ptr(out), rows, width, float(eps), float(offset),
+                                      self._is_bf16(out), self._stream()), "rmsnorm")
+        return out
+
+    def clone(self, x):
+        """A copy of a tensor (a device-to-device copy on the current stream)."""
+        return x.clone()
+
+    def concat_cast(self, a32, b32, out_dtype):
+        """``[a ; b]`` row by row, two 32-bit tensors of one shape, in ``out_dtype``."""
+        self._want(a32, torch.float32, "first rows", 2)
+        self._want(b32, torch.float32, "second rows", 2)
+        if a32.shape != b32.shape:
+            raise KernelLibraryError("concat: the two tensors differ in shape")
+        rows, width = a32.shape
+        out = torch.empty((rows, 2 * width), dtype=out_dtype, device=self.device)
+        self._run(self.lib.mg_concat_cast(_ptr(a32), _ptr(b32), _ptr(out), rows, width, self._is_bf16(out),
+                                          self._stream()), "concat")
+        return out
+
+    def embed_pairs(self, ctx, tok_emb, pair_emb, pos_table, buckets, mul_prev, mul_cur, state, source=None,
+                    previous=None):
+        """Rows of the embedding plus rows of the token-pair table (row ``(previous id * mul_prev + id *
+        mul_cur) mod buckets``, row ``buckets`` for a request's first token) plus rows of the position table.
+        ``state``: int32 ``[slots, 1]``, the last token each request brought (read for a step's first token of
+        a request that has tokens in the cache, written for every request of the step)."""
+        self._want(ctx.token_ids, torch.int32, "token_ids", 1)
+        self._want(ctx.positions, torch.int32, "positions", 1)
+        self._want(tok_emb, None, "tok_emb", 2)
+        self._want(pair_emb, tok_emb.dtype, "pair table", 2)
+        self._want(state, torch.int32, "last tokens", 2)
+        if pos_table is not None:
+            self._want(pos_table, tok_emb.dtype, "pos_table", 2)
+        if source is not None:
+            self._want(source, torch.int32, "token sources", 1)
+            self._want(previous, torch.int32, "previous ids", 1)
+        n, width = ctx.token_ids.numel(), tok_emb.shape[1]
+        if pair_emb.shape != (buckets + 1, width) or (pos_table is not None and pos_table.shape[1] != width):
+            raise KernelLibraryError("embed_pairs: the tables do not fit")
+        if (buckets - 1) * (int(mul_prev) + int(mul_cur)) >= 2 ** 62 or tok_emb.shape[0] * (int(mul_prev) + int(mul_cur)) >= 2 ** 62:
+            raise KernelLibraryError("embed_pairs: the multipliers overflow 64 bits")
+        out = torch.empty((n, width), dtype=torch.float32, device=self.device)
+        self._run(self.lib.mg_embed_pairs(
+            _ptr(ctx.token_ids), _ptr(ctx.positions), _ptr(ctx.token_request), _ptr(ctx.req_q_start), _ptr(ctx.req_q_len),
+            _ptr(ctx.req_ctx_before), _ptr(ctx.req_state_slot), _ptr(tok_emb), _ptr(pair_emb), _ptr(pos_table), _ptr(out),
+            _ptr(state), state.shape[1], n, width, self._is_bf16(tok_emb), _ptr(source), _ptr(previous), tok_emb.shape[0],
+            pos_table.shape[0] if pos_table is not None else 0, previous.numel() if previous is not None else 0,
+            int(buckets), int(mul_prev), int(mul_cur), ctx.req_q_start.numel(), state.shape[0], self._stream()),
+            "embed_pairs")
+        return out
+
+    # ---- mixers with a matrix memory ------------------------------------------------------------------
+    def matrix_memory_scan(self, ctx, mode, proj, q_off, k_off, v_off, n_head, head_dim, v_dim, gates, constant, state):
+        """The scan of a mixer with a matrix memory over the step's tokens, request by request, from and to
+        the requests' state slots.  ``mode`` ``"gla"``: ``gates`` are the decays' pre-activations
+        ``[tokens, n_head * head_dim]`` and ``constant`` is tau; ``"mlstm"``: ``gates`` are the input and
+        forget gates' pre-activations ``[tokens, 2 * n_head]`` and ``constant`` is their cap.  Returns
+        ``(o [tokens, n_head * v_dim] 32-bit, aux)``; ``aux`` (mlstm) holds ``n . q`` and ``m`` per token
+        and head for the division that ``head_norm_gate`` does."""
+        self._want(proj, None, "projection rows", 2)
+        self._want(gates, torch.float32, "gates", 2)
+        self._want(state, torch.float32, "state slots", 2)
+        if mode not in ("gla", "mlstm"):
+            raise KernelLibraryError(f"matrix memory: mode {mode!r}")
+        n = proj.shape[0]
+        if gates.shape[0] != n:
+            raise KernelLibraryError("matrix memory: one row of gates per token")
+        mlstm = mode == "mlstm"
+        out = torch.empty((n, n_head * v_dim), dtype=torch.float32, device=self.device)
+        aux = torch.empty((n, n_head, 2), dtype=torch.float32, device=self.device) if mlstm else None
+        self._run(self.lib.mg_matrix_memory_scan(
+            _ptr(proj), proj.shape[1], q_off, k_off, v_off, _ptr(gates), gates.shape[1], _ptr(ctx.req_q_start),
+            _ptr(ctx.req_q_len), _ptr(ctx.req_ctx_before), _ptr(ctx.req_state_slot), _ptr(state), state.shape[1], _ptr(out),
+            _ptr(aux), ctx.req_q_start.numel(), n, n_head, head_dim, v_dim, float(constant), 1 if mlstm else 0,
+            state.shape[0], self._is_bf16(proj), self._stream()), "matrix memory scan")
+        return out, aux
+
+    def head_norm_gate(self, out32, aux, gate, gain, n_head, v_dim, eps, per_head_gain, gate_activation, out_dtype,
+                       positions=None):
+        """Every head of ``out32`` (divided by ``max(|n . q|, exp(-m)) + 1e-6`` from ``aux`` if given) divided by
+        its root mean square, times ``gain`` (``[v_dim]``, or ``[n_head * v_dim]`` if ``per_head_gain``), times
+        ``silu`` or ``sigmoid`` of ``gate`` (a 2-D view of ``n_head * v_dim`` columns), in ``out_dtype``.  Rows whose
+        ``positions`` entry is negative (padding) become zeros."""
+        self._want(out32, torch.float32, "memory output", 2)
+        self._want(gain, torch.float32, "head gain", 1)
+        n = out32.shape[0]
+        if (gate.dtype != out_dtype or gate.dim() != 2 or gate.stride(1) != 1 or gate.shape != (n, n_head * v_dim)
+                or out32.shape[1] != n_head * v_dim or gain.numel() != (n_head * v_dim if per_head_gain else v_dim)):
+            raise KernelLibraryError("head_norm_gate: shapes do not fit")
+        if gate_activation not in ("silu", "sigmoid"):
+            raise KernelLibraryError(f"head_norm_gate: gate activation {gate_activation!r}")
+        if positions is not None and self._want(positions, torch.int32, "positions", 1).numel() != n:
+            raise KernelLibraryError("head_norm_gate: one position per row")
+        out = torch.empty((n, n_head * v_dim), dtype=out_dtype, device=self.device)
+        self._run(self.lib.mg_head_norm_gate(_ptr(out32), _ptr(aux), _ptr(gate), gate.stride(0), _ptr(gain), _ptr(positions),
+                                             _ptr(out), n, n_head, v_dim, float(eps), 1 if per_head_gain else 0,
+                                             1 if gate_activation == "sigmoid" else 0, self._is_bf16(out), self._stream()),
+                  "head_norm_gate")
         return out
 
     def gather_rows(self, x32, rows):
@@ -652,8 +761,9 @@ class CudaOps:
         return out
 
     def head_prepare(self, proj, n_head, n_kv_head, head_dim, v_dim, q_off, k_off, v_off, unit_norm, eps,
-                     cache, slots, positions, v_other=None, blend=None):
-        """Between a fused projection and the attention, in one kernel: query and key heads of
+                     cache, slots, positions, v_other=None, blend=None, q_gain=None, k_gain=None):
+        """Between a fused projection and the attention, in one kernel (``q_gain`` / ``k_gain``: 32-bit gains of
+        ``head_dim`` numbers on the unit-RMS query and key heads): query and key heads of
         ``proj`` rows divided by their root mean square (``unit_norm``; queries in place), values
         blended with ``v_other`` (a 2-D view whose rows' first columns are the other values of the
         same tokens; ``blend`` a 32-bit scalar on the device), keys and values written to the cache
@@ -679,13 +789,26 @@ class CudaOps:
         self._run(self.lib.mg_head_prepare(
             _ptr(proj), proj.shape[1], proj.shape[0], n_head, n_kv_head, head_dim, v_dim, q_off, k_off, v_off,
             1 if unit_norm else 0, float(eps), *args_other, pages[0], _ptr(positions), pages[1], pages[2],
-            pages[3], pages[4], is_bf16, self._stream()), "head_prepare")
+            pages[3], pages[4], is_bf16, _ptr(self._gain(q_gain, head_dim)), _ptr(self._gain(k_gain, head_dim)),
+            self._stream()), "head_prepare")
 
-    def paged_attention_general(self, q, n_head, n_kv_head, head_dim, v_dim, scale, cache, ctx, gate=None):
+    def _gain(self, gain, size):
+        if gain is not None and self._want(gain, torch.float32, "head gain", 1).numel() != size:
+            raise KernelLibraryError("head_prepare: a gain does not match the head size")
+        return gain
+
+    def paged_attention_general(self, q, n_head, n_kv_head, head_dim, v_dim, scale, cache, ctx, gate=None,
+                                slopes=None, block=None):
         """Causal attention of ``q`` (a 2-D tensor whose rows' first ``n_head * head_dim`` columns
         are the queries) over the pages, keys of size ``head_dim`` and values of size ``v_dim``;
         with ``gate`` (a 2-D view, ``n_head * v_dim`` columns) the output is multiplied by the
-        logistic function of the gate values.  Returns ``[tokens, n_head * v_dim]``."""
+        logistic function of the gate values.  ``slopes`` (32-bit, one per head): ``slope * (i - j)``
+        is taken off the score of query ``i`` and key ``j``; ``block``: a query sees only the keys
+        of its own block of that many positions.  Returns ``[tokens, n_head * v_dim]``."""
+        if slopes is not None and self._want(slopes, torch.float32, "slopes", 1).numel() != n_head:
+            raise KernelLibraryError("attention: one slope per head")
+        block = int(block or 0)
+        biased = slopes is not None or block > 0
         self._want(q, cache.k_pages.dtype, "queries", 2)
         table = self._want(ctx.block_tables[cache.group], torch.int32, "block_table", 2)
         n = q.shape[0]
@@ -694,7 +817,7 @@ class CudaOps:
             raise KernelLibraryError("attention: the gate does not fit the heads")
         out = torch.empty((n, n_head * v_dim), dtype=q.dtype, device=self.device)
         work = getattr(ctx, "extra", {}).get(self._attention_tiles_name(n_head)) if hasattr(ctx, "extra") else None
-        if (q.dtype == torch.bfloat16 and work is not None and work.shape[0] > 0 and head_dim == v_dim
+        if (q.dtype == torch.bfloat16 and work is not None and work.shape[0] > 0 and head_dim == v_dim and not biased
                 and head_dim in self.PREFILL_TC_HEAD_DIMS and self.use_tensor_cores and self.use_prefill_tc
                 and not getattr(ctx, "decode_only", False)):
             # equal key and value sizes that the tcgen05 prompt attention takes: its tiles, with the
@@ -714,7 +837,7 @@ class CudaOps:
             if code != library.UNSUPPORTED:
                 self._run(code, "paged_attention (prefill, tensor cores)")
                 return out
-        if q.dtype == torch.bfloat16 and self.use_tensor_cores and self.use_mma_attention:
+        if q.dtype == torch.bfloat16 and self.use_tensor_cores and self.use_mma_attention and not biased:
             # bfloat16: tiles of (token, head) rows on the warp-level tensor cores; single tokens
             # with their keys cut into ranges that a second kernel merges
             single = bool(getattr(ctx, "decode_only", False))
@@ -749,8 +872,8 @@ class CudaOps:
             _ptr(q), q.shape[1], _ptr(cache.k_pages), _ptr(cache.v_pages), _ptr(table), _ptr(ctx.token_request),
             _ptr(ctx.positions), _ptr(out), n, n_head, n_kv_head, head_dim, v_dim, _ptr(gate),
             gate.stride(0) if gate is not None else 0, cache.page_tokens, table.shape[1], int(cache.window or 0),
-            float(scale), cache.k_pages.shape[0], table.shape[0], self._is_bf16(q), self._stream()),
-            "paged_attention (general)")
+            float(scale), cache.k_pages.shape[0], table.shape[0], self._is_bf16(q), _ptr(slopes), block,
+            self._stream()), "paged_attention (general)")
         return out
 
     # ---- routed experts ---------------------------------------------------------------------------
@@ -777,7 +900,38 @@ class CudaOps:
                                         self._stream()), "moe route")
         return ids, weights, gate
 
-    def moe_experts_residual(self, y, ids, weights, w_in, w_out, residual32):
+    def moe_route_scored(self, y, router_weight, gate_weight, positions, top, scoring, correction, groups, scale):
+        """As ``moe_route`` with a score per expert: ``scoring`` ``"sigmoid"`` (weights ``scale * sigmoid(z)``
+        of the chosen, not renormalised) or ``"softmax_top"`` (``scale`` times the softmax over the chosen
+        logits); ``correction`` (32-bit, one per expert, or None) is added for the choice only; ``groups``
+        ``(count, keep)`` or None: only experts of the ``keep`` best of ``count`` equal groups of neighbours
+        (a group's score: the sum of its two largest choice scores) can be chosen."""
+        self._want(y, None, "router input", 2)
+        self._want(router_weight, torch.float32, "router weight", 2)
+        n, width = y.shape
+        experts = router_weight.shape[0]
+        if router_weight.shape[1] != width or not 0 < top <= experts:
+            raise KernelLibraryError("moe_route: shapes do not fit")
+        if correction is not None and self._want(correction, torch.float32, "correction", 1).numel() != experts:
+            raise KernelLibraryError("moe_route: one correction per expert")
+        if scoring not in ("sigmoid", "softmax_top"):
+            raise KernelLibraryError(f"moe_route: scoring {scoring!r}")
+        count, keep = groups if groups is not None else (0, 0)
+        ids = torch.empty((n, top), dtype=torch.int32, device=self.device)
+        weights = torch.empty((n, top), dtype=torch.float32, device=self.device)
+        gate = None
+        if gate_weight is not None:
+            self._want(gate_weight, torch.float32, "gate weight")
+            if gate_weight.numel() != width:
+                raise KernelLibraryError("moe_route: the gate's weights do not fit the width")
+            gate = torch.empty((n,), dtype=torch.float32, device=self.device)
+        self._run(self.lib.mg_moe_route_scored(_ptr(y), _ptr(router_weight), _ptr(gate_weight), _ptr(correction),
+                                               _ptr(positions), _ptr(ids), _ptr(weights), _ptr(gate), n, width, experts,
+                                               top, 1 if scoring == "sigmoid" else 0, int(count), int(keep), float(scale),
+                                               self._is_bf16(y), self._stream()), "moe route (scored)")
+        return ids, weights, gate
+
+    def moe_experts_residual(self, y, ids, weights, w_in, w_out, residual32, activation="silu", limit=0.0):
         """``residual32[t] += sum_k weights[t, k] * expert(ids[t, k])(y[t])`` with expert e as
         ``w_out[e] @ (silu(w_in[e][:F] @ y) * (w_in[e][F:] @ y))``; ``w_in`` [E, 2F, C], ``w_out``
         [E, C, F].  Tokens are grouped by expert on the device; the host never learns the counts."""
@@ -793,6 +947,7 @@ class CudaOps:
             raise KernelLibraryError("moe_experts: shapes do not fit")
         entries = n * top
         is_bf16 = self._is_bf16(y)
+        act = GATED_ACTIVATIONS[activation]
         offsets = torch.empty((experts + 1,), dtype=torch.int32, device=self.device)
         slot_entry = torch.empty((entries,), dtype=torch.int32, device=self.device)
         entry_slot = torch.empty((entries,), dtype=torch.int32, device=self.device)
@@ -800,18 +955,21 @@ class CudaOps:
                                         self._stream()), "moe group")
         hidden = torch.empty((entries, inner), dtype=y.dtype, device=self.device)
         self._run(self.lib.mg_moe_gemm(_ptr(y), width, _ptr(w_in), _ptr(offsets), _ptr(slot_entry), top, None,
-                                       _ptr(hidden), experts, n, inner, width, n, 1, is_bf16, self._stream()),
+                                       _ptr(hidden), experts, n, inner, width, n, 1, is_bf16, act, float(limit),
+                                       self._stream()),
                   "moe experts (in)")
         out = torch.empty((entries, width), dtype=torch.float32, device=self.device)
         self._run(self.lib.mg_moe_gemm(_ptr(hidden), inner, _ptr(w_out), _ptr(offsets), _ptr(slot_entry), top,
-                                       _ptr(weights), _ptr(out), experts, n, width, inner, entries, 0, is_bf16,
+                                       _ptr(weights), _ptr(out), experts, n, width, inner, entries, 0, is_bf16, 0, 0.0,
                                        self._stream()), "moe experts (out)")
         self._run(self.lib.mg_moe_combine(_ptr(out), _ptr(entry_slot), top, _ptr(residual32), n, width, entries,
                                           self._stream()), "moe combine")
 
-    def glu(self, gate_up, row_scale=None):
+    def glu(self, gate_up, row_scale=None, activation="silu", limit=0.0):
         """``silu(gate_up[:, :F]) * gate_up[:, F:]``, each row times ``row_scale`` (32-bit ``[rows]``)
-        if given; the result has the input's dtype."""
+        if given; the result has the input's dtype.  ``activation``: ``silu``, ``gelu_tanh`` (in place of
+        silu) or ``clamped_swish`` (``g * sigmoid(1.702 g) * (u + 1)`` with ``g = min(gate, limit)``,
+        ``u = clamp(up, -limit, limit)``)."""
         self._want(gate_up, None, "gate and up features", 2)
         rows, two_f = gate_up.shape
         if two_f % 2:
@@ -820,7 +978,7 @@ class CudaOps:
             raise KernelLibraryError("glu: one scale per row")
         out = torch.empty((rows, two_f // 2), dtype=gate_up.dtype, device=self.device)
         self._run(self.lib.mg_glu(_ptr(gate_up), _ptr(row_scale), _ptr(out), rows, two_f // 2, self._is_bf16(gate_up),
-                                  self._stream()), "glu")
+                                  GATED_ACTIVATIONS[activation], float(limit), self._stream()), "glu")
         return out
 
     # ---- sampling -------------------------------------------------------------------------------

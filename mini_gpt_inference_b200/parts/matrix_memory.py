@@ -66,7 +66,8 @@ class _MatrixMemoryMixer(Mixer):
     def _finish(self, ctx, proj, memory_out, aux, residual32, per_head_gain: bool, gate_activation: str):
         gate = proj[:, self.g_off: self.g_off + self.v_width]
         heads = ctx.ops.head_norm_gate(memory_out, aux, gate, self.norm_gain, self.n_head, self.v_head_dim,
-                                       self.eps, per_head_gain, gate_activation, ctx.act_dtype)
+                                       self.eps, per_head_gain, gate_activation, ctx.act_dtype,
+                                       positions=ctx.positions)
         ctx.ops.linear_residual(heads, self.out_weight, None, residual32)
 
 

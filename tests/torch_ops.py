@@ -258,7 +258,8 @@ class TorchOps:
                 flat[n_head * cols * head_dim:] = m
         return out.reshape(n, n_head * v_dim), aux
 
-    def head_norm_gate(self, out32, aux, gate, gain, n_head, v_dim, eps, per_head_gain, gate_activation, out_dtype):
+    def head_norm_gate(self, out32, aux, gate, gain, n_head, v_dim, eps, per_head_gain, gate_activation, out_dtype,
+                       positions=None):
         n = out32.shape[0]
         o = out32.view(n, n_head, v_dim)
         if aux is not None:
