@@ -52,7 +52,16 @@ struct AttnParams {
     int tile_tokens;              // tiles: tokens per tile
     int splits, split_keys;       // split: ranges of keys per token
     float scale_log2;             // scale * log2(e)
+    const float* slopes;          // [H] or null: slope_h * (i - j) is taken off the score of query i and key j
+    int block;                    // > 0: a query sees only the keys of its own block of this many positions
 };
+
+// The first key that a query at `pos` sees: the window's, raised to the first position of the query's block.
+__device__ __forceinline__ int first_visible(const AttnParams& p, int pos) {
+    int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    if (p.block > 0) lo = max(lo, pos / p.block * p.block);
+    return lo;
+}
 
 __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -142,7 +151,8 @@ __device__ __forceinline__ void load_q(uint32_t (&qf)[DP / 16][4], const bf16* q
 template <int DP, int DVP, int NT>
 __device__ __forceinline__ void attend(const uint32_t (&qf)[DP / 16][4], const bf16* ks, const bf16* vs, int k_first,
                                        int j_first, const int (&pos)[2], const int (&lo)[2], bool all_visible,
-                                       float scale_log2, float (&m)[2], float (&l)[2], float (&o)[DVP / 8][4], int lane) {
+                                       float scale_log2, float (&m)[2], float (&l)[2], float (&o)[DVP / 8][4], int lane,
+                                       const float (&slope_log2)[2], bool biased) {
     float s[NT][4];
 #pragma unroll
     for (int n = 0; n < NT; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
@@ -159,13 +169,24 @@ __device__ __forceinline__ void attend(const uint32_t (&qf)[DP / 16][4], const b
     // masks and the block's maximum per row (all_visible, the same for the whole warp: every row of
     // the warp sees every key of these, nothing to compare)
     float bm[2] = {-INFINITY, -INFINITY};
-    if (all_visible) {
+    if (all_visible && !biased) {
 #pragma unroll
         for (int n = 0; n < NT; ++n)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 s[n][e] *= scale_log2;
                 bm[e >> 1] = fmaxf(bm[e >> 1], s[n][e]);
+            }
+    } else if (biased) {
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int j = j_first + n * 8 + 2 * (lane & 3) + (e & 1), r = e >> 1;
+                const float v = (j <= pos[r] && j >= lo[r]) ? fmaf(s[n][e], scale_log2, -slope_log2[r] * (float)(pos[r] - j))
+                                                            : -INFINITY;
+                s[n][e] = v;
+                bm[r] = fmaxf(bm[r], v);
             }
     } else {
 #pragma unroll
@@ -257,7 +278,7 @@ attention_tiles_kernel(const AttnParams p) {
     int hi = p.positions[first + count - 1], lo_tile = 0;
     if (hi < 0) return;                                     // padding
     if (!MG_GUARDED(attention_mma, MG_GUARD_POSITION, hi, (long long)p.max_pages * p.page_tokens)) hi = 0;
-    if (p.window > 0) lo_tile = max(0, p.positions[first] - p.window + 1);
+    if (p.window > 0 || p.block > 0) lo_tile = first_visible(p, max(0, p.positions[first]));
     const int* table = p.block_table + (size_t)request * p.max_pages;
 
     // this lane's two rows
@@ -271,9 +292,11 @@ attention_tiles_kernel(const AttnParams p) {
         token[r] = first + (live ? t : 0);
         head[r] = kv_head * group + row % group;
         pos[r] = live ? p.positions[token[r]] : -1;
-        lo[r] = (p.window > 0 && pos[r] >= 0) ? max(0, pos[r] - p.window + 1) : 0;
+        lo[r] = pos[r] >= 0 ? first_visible(p, pos[r]) : 0;
         qrow[r] = live ? p.q + (size_t)token[r] * p.q_stride + (size_t)head[r] * p.d : nullptr;
     }
+    const bool biased = p.slopes != nullptr;
+    const float slope_log2[2] = {biased ? p.slopes[head[0]] * LOG2E : 0.f, biased ? p.slopes[head[1]] * LOG2E : 0.f};
     uint32_t qf[DP / 16][4];
     load_q<DP>(qf, qrow[0], qrow[1], p.d, lane);
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f}, o[DVP / 8][4];
@@ -284,7 +307,7 @@ attention_tiles_kernel(const AttnParams p) {
     const int warp_hi = (warp * 16) / group < count ? p.positions[first + warp_last_token] : -1;
     // blocks that all rows of the warp see whole: up to the warp's first token, from the last one's window on
     const int warp_first_pos = (warp * 16) / group < count ? p.positions[first + (warp * 16) / group] : -1;
-    const int warp_max_lo = (p.window > 0 && warp_hi >= 0) ? max(0, warp_hi - p.window + 1) : 0;
+    const int warp_max_lo = warp_hi >= 0 ? first_visible(p, warp_hi) : 0;
 
     // two buffers take turns: the next block's copies are in flight while this one is multiplied
     const int j_begin = (lo_tile / KB) * KB;
@@ -304,7 +327,8 @@ attention_tiles_kernel(const AttnParams p) {
         __syncthreads();
         if (j0 <= warp_hi)
             attend<DP, DVP, 8>(qf, ks + buf * STAGE, vs + buf * STAGE, 0, j0, pos, lo,
-                               j0 + KB - 1 <= warp_first_pos && j0 >= warp_max_lo, p.scale_log2, m, l, o, lane);
+                               j0 + KB - 1 <= warp_first_pos && j0 >= warp_max_lo, p.scale_log2, m, l, o, lane, slope_log2,
+                               biased);
         __syncthreads();                                    // the buffer is free for the block after the next
     }
 #pragma unroll
@@ -346,7 +370,7 @@ attention_split_kernel(const AttnParams p) {
     int position = p.positions[token];
     const bool padding = position < 0;
     if (!padding && !MG_GUARDED(attention_mma, MG_GUARD_POSITION, position, (long long)p.max_pages * p.page_tokens)) position = 0;
-    const int lo_row = (p.window > 0 && !padding) ? max(0, position - p.window + 1) : 0;
+    const int lo_row = padding ? 0 : first_visible(p, position);
     const int first = (lo_row / KB) * KB + split * p.split_keys;         // ranges start at the window's block
     const int last = min(position, first + p.split_keys - 1);
     // ranges that hold keys of this token; the others have nothing to do (the grid is sized for the
@@ -376,6 +400,9 @@ attention_split_kernel(const AttnParams p) {
             lo[r] = lo_row;
             qrow[r] = has_row ? p.q + (size_t)token * p.q_stride + (size_t)(kv_head * group + row) * p.d : nullptr;
         }
+        const bool biased = p.slopes != nullptr;
+        const float slope_log2[2] = {biased && row0 < group ? p.slopes[kv_head * group + row0] * LOG2E : 0.f,
+                                     biased && row0 + 8 < group ? p.slopes[kv_head * group + row0 + 8] * LOG2E : 0.f};
         uint32_t qf[DP / 16][4];
         load_q<DP>(qf, qrow[0], qrow[1], p.d, lane);
         const int page_shift = (p.page_tokens & (p.page_tokens - 1)) == 0 ? __ffs(p.page_tokens) - 1 : -1;
@@ -394,7 +421,7 @@ attention_split_kernel(const AttnParams p) {
             __syncthreads();
             if (j0 + warp * 16 <= last)
                 attend<DP, DVP, 2>(qf, ks + buf * STAGE, vs + buf * STAGE, warp * 16, j0 + warp * 16, pos, lo, false,
-                                   p.scale_log2, m, l, o, lane);
+                                   p.scale_log2, m, l, o, lane, slope_log2, biased);
             __syncthreads();
         }
     }
@@ -488,7 +515,7 @@ __global__ void attention_merge_kernel(const AttnParams p) {
         for (int c = threadIdx.x; c < p.dv; c += blockDim.x) orow[c] = __float2bfloat16_rn(0.f);
         return;
     }
-    const int lo_row = p.window > 0 ? max(0, position - p.window + 1) : 0;
+    const int lo_row = first_visible(p, position);
     const int live = min(min(p.splits, MERGE_MAX), (position - (lo_row / KB) * KB) / p.split_keys + 1);   // ranges that hold keys
     for (int s = threadIdx.x; s < live; s += blockDim.x) weight[s] = p.part_ml[(base + s) * 2];
     __syncthreads();
@@ -560,13 +587,13 @@ MG_API long long mg_attention_mma_scratch_floats(int n_tokens, int n_head, int d
 // single_tokens = 1: every token is alone in its request's step (splits ranges of split_keys keys,
 // scratch of mg_attention_mma_scratch_floats floats; counters: n_tokens * n_kv_head zeros that are left
 // as zeros, or null to merge the ranges in a second kernel); 0: n_tiles tiles of tile_tokens tokens, found
-// from req_q_start / req_q_len.  Returns MG_ERR_UNSUPPORTED for sizes it does not take.
+// from req_q_start / req_q_len.  slopes: [n_head] 32-bit or null; key_block <= 0: no block mask.  Returns MG_ERR_UNSUPPORTED for sizes it does not take.
 MG_API int mg_attention_mma(const void* q, int q_stride, const void* k_pages, const void* v_pages, const int* block_table,
                             const int* token_request, const int* positions, const int* req_q_start,
                             const int* req_q_len, const void* gate, int gate_stride, void* out, float* scratch,
                             int* counters, int n_tokens, int n_requests, int n_head, int n_kv_head, int d, int dv, int page_tokens,
                             int max_pages, int window, float scale, int num_pages, int single_tokens, int n_tiles,
-                            int tile_tokens, int splits, int split_keys, void* stream) {
+                            int tile_tokens, int splits, int split_keys, const float* slopes, int key_block, void* stream) {
     if (n_tokens == 0) return MG_OK;
     MG_REQUIRE(n_tokens > 0 && n_head > 0 && n_kv_head > 0 && n_head % n_kv_head == 0 && page_tokens > 0 && max_pages > 0,
                "attention: bad sizes");
@@ -583,6 +610,7 @@ MG_API int mg_attention_mma(const void* q, int q_stride, const void* k_pages, co
     p.n_tokens = n_tokens; p.n_requests = n_requests; p.n_head = n_head; p.n_kv_head = n_kv_head; p.d = d; p.dv = dv;
     p.page_tokens = page_tokens; p.max_pages = max_pages; p.window = window > 0 ? window : 0; p.num_pages = num_pages;
     p.tile_tokens = tile_tokens; p.splits = splits; p.split_keys = split_keys; p.scale_log2 = scale * LOG2E;
+    p.slopes = slopes; p.block = key_block > 0 ? key_block : 0;
     if (single_tokens) {
         MG_REQUIRE(scratch != nullptr && splits > 0 && splits <= 65535 && split_keys > 0 && split_keys % KB == 0,
                    "attention: the ranges of keys want scratch and sizes that are multiples of %d", KB);

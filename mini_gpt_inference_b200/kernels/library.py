@@ -35,7 +35,7 @@ _SIGNATURES = {
     "mg_head_norm_gate": [_P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _F, _I, _I, _I, _P],
     "mg_moe_route_scored": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "mg_attention_mma": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F,
-                         _I, _I, _I, _I, _I, _I, _P],
+                         _I, _I, _I, _I, _I, _I, _P, _I, _P],
     "mg_moe_route": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "mg_moe_group": [_P, _I, _I, _P, _P, _P, _P],
     "mg_moe_gemm": [_P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P],

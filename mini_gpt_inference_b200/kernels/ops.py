@@ -837,7 +837,7 @@ class CudaOps:
             if code != library.UNSUPPORTED:
                 self._run(code, "paged_attention (prefill, tensor cores)")
                 return out
-        if q.dtype == torch.bfloat16 and self.use_tensor_cores and self.use_mma_attention and not biased:
+        if q.dtype == torch.bfloat16 and self.use_tensor_cores and self.use_mma_attention:
             # bfloat16: tiles of (token, head) rows on the warp-level tensor cores; single tokens
             # with their keys cut into ranges that a second kernel merges
             single = bool(getattr(ctx, "decode_only", False))
@@ -846,7 +846,10 @@ class CudaOps:
             args = None
             if single:
                 keys = self.lib.mg_attention_mma_split_keys(int(ctx.max_ctx_after))
-                splits = max(1, -(-int(ctx.max_ctx_after) // keys))
+                # (with a block mask a token's keys begin at its block: ranges are counted from the key
+                # block of 64 that holds the block's first position)
+                span = int(ctx.max_ctx_after) if block <= 0 else min(int(ctx.max_ctx_after), block + 64)
+                splits = max(1, -(-span // keys))
                 floats = self.lib.mg_attention_mma_scratch_floats(n, n_head, v_dim, splits)
                 scratch = torch.empty((floats,), dtype=torch.float32, device=self.device)
                 # (measured at batch 8, context 2,048: the ranges merged by a second kernel, 0.273 ms a
@@ -862,7 +865,7 @@ class CudaOps:
                     _ptr(ctx.positions), _ptr(getattr(ctx, "req_q_start", None)), _ptr(getattr(ctx, "req_q_len", None)),
                     _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(out), args[0], args[1], n, table.shape[0],
                     n_head, n_kv_head, head_dim, v_dim, cache.page_tokens, table.shape[1], int(cache.window or 0),
-                    float(scale), cache.k_pages.shape[0], *args[2:], self._stream())
+                    float(scale), cache.k_pages.shape[0], *args[2:], _ptr(slopes), block, self._stream())
                 if code != library.UNSUPPORTED:
                     self._run(code, "paged_attention (tensor cores, general)")
                     if single and args[1] is None:

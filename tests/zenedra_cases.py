@@ -98,10 +98,12 @@ PAGE_TOKENS = {"A": 8, "B": 16, "C": 4, "D": 16}
 DECAY_RANK = {"A": 4, "B": 7, "C": 16, "D": 8}
 
 
-def random_weights(raw: dict, seed: int, dtype=torch.float32, rank: int = 5, sharp: float = 1.0) -> dict:
+def random_weights(raw: dict, seed: int, dtype=torch.float32, rank: int = 5, sharp: float = 1.0,
+                   as_bfloat16: bool = False) -> dict:
     """Weights with unit-variance activations: matrices ``N(0, 1 / inputs)``, output projections smaller by the
     depth, norm weights and biases ``N(0, 0.3)``, embeddings ``N(0, 1)``.  ``sharp`` scales the query projections
-    of the attention layers, so that a softmax leans on few keys."""
+    of the attention layers, so that a softmax leans on few keys.  ``as_bfloat16``: every number is one that
+    bfloat16 holds (an engine that computes in bfloat16 and the plain side then use the same weights)."""
     gen = torch.Generator().manual_seed(seed)
     c = raw["width"]
     depth = len(plain_zenedra.run_order(raw))
@@ -160,6 +162,8 @@ def random_weights(raw: dict, seed: int, dtype=torch.float32, rank: int = 5, sha
         for q, ff in units:
             w[q + "gate"], w[q + "up"] = mat(ff, c, 1.5), mat(ff, c, 1.5)
             w[q + "down"] = mat(c, ff, out_scale)
+    if as_bfloat16:
+        w = {k: v.to(torch.bfloat16).float() for k, v in w.items()}
     return {k: v.to(dtype).contiguous() for k, v in w.items()}
 
 
@@ -177,10 +181,16 @@ def plain_greedy(raw: dict, tensors: dict, prompt, new_tokens: int) -> list[int]
     return plain_zenedra.greedy(prompt, tensors, raw, new_tokens)
 
 
+def relative_error(got: torch.Tensor, want: torch.Tensor) -> torch.Tensor:
+    """Per row: the largest difference of the logits over the row's own spread."""
+    want = want.double()
+    return (got.double().cpu() - want).abs().amax(-1) / want.std(-1)
+
+
 def assert_rows_close(got, want, tol, what: str, places=None) -> None:
-    diff = (got.double().cpu() - want.double()).abs().amax(dim=-1)
-    bad = (diff > tol).nonzero()
+    err = relative_error(got, want)
+    bad = (~(err <= tol)).nonzero()
     if bad.numel():
         i = int(bad[0])
-        where = places[i] if places is not None else i
-        raise AssertionError(f"{what}: first wrong logits at {where}: |diff| = {float(diff[i]):.3e} > {tol:.1e}")
+        raise AssertionError(f"{what}: first wrong logits at {places[i] if places is not None else i}: "
+                             f"error {float(err[i]):.3e} of the row's spread > {tol:.1e}")
