@@ -24,6 +24,8 @@ tokens each) through ``LLMEngine.generate``, wall clock: the scheduler's mixed b
 and one 2,048-token prompt (an event pair around every launch; the reference sums its kernels' time
 from a profiler's trace, bench/bench_kernels.py:71-116).
 
+``--only zenedra`` prints a line of its own as well: the Zenedra decoder (layers of one mixer kind each, then
+mixed with a loop and routed experts) beside the two other designs at equal sizes.
 ``--only designs`` prints a line of its own: the Fakilorn decoder beside this decoder at equal width,
 depth, hidden width and vocabulary (random weights, two sizes): a 2,048-token prompt step, decode
 steps at the headline batch with contexts near 2,048, and the device time of every exported function
@@ -87,7 +89,7 @@ def parse_args():
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--page-tokens", type=int, default=64)
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and prefill")
-    ap.add_argument("--only", choices=["all", "decode", "prefill", "serve", "kernels", "designs"], default="all",
+    ap.add_argument("--only", choices=["all", "decode", "prefill", "serve", "kernels", "designs", "zenedra"], default="all",
                     help="a small case for profilers: only the device-timed decode steps, or only "
                          "the 2,048-token prefill (the printed line is then partial); serve: 64 "
                          "requests with prompts of 16 to 512 tokens and 256 generated tokens each "
@@ -466,86 +468,153 @@ def _fakilorn_raw(sz: dict, dim: int, vdim: int, moe: bool) -> dict:
             "embedding": {"scale": 1.0}, "logit_scale": 1.0, "norm": {"eps": 1e-5}}
 
 
-def compare_designs(args) -> dict:
+def _measure_design(args, ops, flush, name, cfg, batch, context, prompt_len) -> dict:
+    """One model with random weights: a prompt of ``prompt_len`` tokens, decode steps of ``batch`` requests at
+    ``context``, and the device time of every exported function in both (launches issued one by one)."""
     import torch
 
-    from mini_gpt_inference_b200 import FakilornConfig, GPTConfig
     from mini_gpt_inference_b200.config import lookup
     from mini_gpt_inference_b200.engine.build import load_model, make_runner
     from mini_gpt_inference_b200.engine.runner import StepEntry
-    from mini_gpt_inference_b200.kernels.ops import default_ops
     from mini_gpt_inference_b200.kernels.timing import LaunchTimer
     from mini_gpt_inference_b200.parts import DecoderModel
     from mini_gpt_inference_b200.weights import random_tensors
+
+    model = DecoderModel(lookup(cfg.architecture).describe(cfg))
+    store = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
+    loaded = load_model(config=cfg, tensors=random_tensors(model, 0, store), dtype=args.dtype, device="cuda:0")
+    pt = args.page_tokens
+    runner = make_runner(loaded, ops, pt, (batch + 1) * (context // pt + 2), batch + 1)
+    gen = torch.Generator().manual_seed(1)
+    vocab = cfg.vocab_size
+
+    def prompt(n):
+        return torch.randint(0, vocab, (n,), generator=gen).tolist()
+
+    def timed(fn, reps):
+        times = []
+        for rep in range(reps + 3):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            if rep >= 3:
+                times.append(a.elapsed_time(b))
+        return statistics.median(times)
+
+    def one_prompt():
+        runner.step([StepEntry("p", prompt(prompt_len), [prompt_len - 1])])
+        runner.finish("p")
+
+    row = {"model": name, "parameters_m": round(cfg.num_parameters() / 1e6, 1)}
+    pre_ms = timed(one_prompt, 5)
+    row["prefill_ms"] = round(pre_ms, 3)
+    row["prefill_tok_s"] = round(prompt_len / (pre_ms * 1e-3))
+    rids = [f"d{i}" for i in range(batch)]
+    for rid in rids:
+        runner.step([StepEntry(rid, prompt(context - 40), [])])
+    dec_ms = timed(lambda: runner.step([StepEntry(rid, [7], [0]) for rid in rids]), 24)
+    row["decode_ms_per_step"] = round(dec_ms, 4)
+    row["decode_tok_s"] = round(batch / (dec_ms * 1e-3))
+    runner.use_cuda_graphs = False
+    for what, fn in (("decode", lambda: runner.step([StepEntry(rid, [7], [0]) for rid in rids])), ("prefill", one_prompt)):
+        for rep in range(3):
+            with LaunchTimer(ops) as timer:
+                fn()
+            rows = timer.summary()
+        row[what + "_functions"] = [{"function": r.name, "calls": r.calls, "total_us": round(r.total_us, 1),
+                                     "mean_us": round(r.mean_us, 2)} for r in rows]
+    for rid in rids:
+        runner.finish(rid)
+    ops.check_status()
+    del runner, loaded
+    torch.cuda.empty_cache()
+    return row
+
+
+def _gpt_like(sz: dict, context: int):
+    from mini_gpt_inference_b200 import GPTConfig
+
+    return GPTConfig.from_dict(dict(vocab_size=sz["vocab"], n_positions=context + 64, n_layer=sz["layers"],
+                                    n_head=sz["heads"], n_embd=sz["width"], n_inner=sz["ff"], bias=False,
+                                    layer_norm_epsilon=1e-5))
+
+
+def compare_designs(args) -> dict:
+    import torch
+
+    from mini_gpt_inference_b200 import FakilornConfig
+    from mini_gpt_inference_b200.kernels.ops import default_ops
 
     ops = default_ops("cuda:0")
     batch, context, prompt_len = args.batch, 2048, PREFILL_TOKENS
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda:0")
     out = {"impl": "ours", "partial": "designs side by side", "dtype": args.dtype, "batch": batch, "context": context,
            "prompt": prompt_len, "rows": []}
-
-    def measure(name, cfg):
-        model = DecoderModel(lookup(cfg.architecture).describe(cfg))
-        store = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
-        loaded = load_model(config=cfg, tensors=random_tensors(model, 0, store), dtype=args.dtype, device="cuda:0")
-        pt = args.page_tokens
-        runner = make_runner(loaded, ops, pt, (batch + 1) * (context // pt + 2), batch + 1)
-        gen = torch.Generator().manual_seed(1)
-        vocab = cfg.vocab_size
-
-        def prompt(n):
-            return torch.randint(0, vocab, (n,), generator=gen).tolist()
-
-        def timed(fn, reps):
-            times = []
-            for rep in range(reps + 3):
-                flush.zero_()
-                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a.record()
-                fn()
-                b.record()
-                torch.cuda.synchronize()
-                if rep >= 3:
-                    times.append(a.elapsed_time(b))
-            return statistics.median(times)
-
-        def one_prompt():
-            runner.step([StepEntry("p", prompt(prompt_len), [prompt_len - 1])])
-            runner.finish("p")
-
-        row = {"model": name, "parameters_m": round(cfg.num_parameters() / 1e6, 1)}
-        pre_ms = timed(one_prompt, 5)
-        row["prefill_ms"] = round(pre_ms, 3)
-        row["prefill_tok_s"] = round(prompt_len / (pre_ms * 1e-3))
-        rids = [f"d{i}" for i in range(batch)]
-        for rid in rids:
-            runner.step([StepEntry(rid, prompt(context - 40), [])])
-        dec_ms = timed(lambda: runner.step([StepEntry(rid, [7], [0]) for rid in rids]), 24)
-        row["decode_ms_per_step"] = round(dec_ms, 4)
-        row["decode_tok_s"] = round(batch / (dec_ms * 1e-3))
-        runner.use_cuda_graphs = False
-        for what, fn in (("decode", lambda: runner.step([StepEntry(rid, [7], [0]) for rid in rids])), ("prefill", one_prompt)):
-            for rep in range(3):
-                with LaunchTimer(ops) as timer:
-                    fn()
-                rows = timer.summary()
-            row[what + "_functions"] = [{"function": r.name, "calls": r.calls, "total_us": round(r.total_us, 1),
-                                         "mean_us": round(r.mean_us, 2)} for r in rows]
-        for rid in rids:
-            runner.finish(rid)
-        ops.check_status()
-        del runner, loaded
-        torch.cuda.empty_cache()
-        return row
-
     for size_name, sz in DESIGN_SIZES.items():
-        gpt = GPTConfig.from_dict(dict(vocab_size=sz["vocab"], n_positions=context + 64, n_layer=sz["layers"],
-                                       n_head=sz["heads"], n_embd=sz["width"], n_inner=sz["ff"], bias=False,
-                                       layer_norm_epsilon=1e-5))
-        out["rows"].append(measure(f"gpt2-style {size_name}", gpt))
+        out["rows"].append(_measure_design(args, ops, flush, f"gpt2-style {size_name}", _gpt_like(sz, context), batch,
+                                           context, prompt_len))
         for dim, vdim, moe in ((64, 64, False), (64, 64, True), (96, 64, True)):
             cfg = FakilornConfig.from_dict(_fakilorn_raw(sz, dim, vdim, moe))
-            out["rows"].append(measure(f"fakilorn {size_name} heads {dim}/{vdim} {'dense+experts' if moe else 'dense'}", cfg))
+            out["rows"].append(_measure_design(
+                args, ops, flush, f"fakilorn {size_name} heads {dim}/{vdim} {'dense+experts' if moe else 'dense'}", cfg,
+                batch, context, prompt_len))
+    return out
+
+
+# ``--only zenedra``: the Zenedra decoder beside the two other designs at equal width, depth, head count and
+# vocabulary (random weights): layers of one mixer kind each with gated dense feed-forwards (so that every
+# mixer's kernels can be read off alone), then the three kinds mixed with a loop over two layers and routed
+# experts.  Heads of 64 key channels; the matrix memories have half as many heads with values of 128.
+def _zenedra_raw(sz: dict, kinds: list, moe: bool, loop: bool, context: int) -> dict:
+    heads = sz["heads"]
+    mixers = {
+        "attention": {"heads": heads, "kv_heads": sz["kv_heads"], "dim": 64, "vdim": 64, "scale": 0.125,
+                      "mask": {"size": 512}},
+        "gla": {"heads": heads // 2, "dim": 64, "vdim": 128, "tau": 16.0},
+        "mlstm": {"heads": heads // 2, "dim": 64, "vdim": 128, "gate_cap": 15.0},
+    }
+    dense = {"kind": "dense", "ff": sz["ff"] * 2 // 3 // 64 * 64}      # three matrices where the others have two
+    routed = {"kind": "moe", "expert": {"ff": sz["expert_ff"], "limit": 7.0},
+              "router": {"experts": sz["experts"], "top": sz["top"], "scale": 2.5, "groups": {"count": 4, "keep": 2}},
+              "shared": {"ff": sz["shared_ff"], "limit": 7.0}}
+    layers = [{"type": kind, "mixer": dict(mixers[kind]), "mlp": routed if (moe and i % 2) else dense}
+              for i, kind in enumerate(kinds)]
+    raw = {"architecture": "Zenedra", "vocab": sz["vocab"], "width": sz["width"], "max_positions": context + 64,
+           "layers": layers, "norm": {"eps": 1e-5}, "embedding": {"bigram": {"buckets": 50021, "mul_prev": 1009, "mul_cur": 7}}}
+    if loop:
+        raw["loop"] = {"start": 1, "stop": 3, "times": 2}
+    return raw
+
+
+def compare_zenedra(args) -> dict:
+    import torch
+
+    from mini_gpt_inference_b200 import FakilornConfig, ZenedraConfig
+    from mini_gpt_inference_b200.kernels.ops import default_ops
+
+    ops = default_ops("cuda:0")
+    batch, context, prompt_len = args.batch, 2048, PREFILL_TOKENS
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda:0")
+    out = {"impl": "ours", "partial": "zenedra beside the other designs", "dtype": args.dtype, "batch": batch,
+           "context": context, "prompt": prompt_len, "rows": []}
+    for size_name, sz in DESIGN_SIZES.items():
+        n = sz["layers"]
+        out["rows"].append(_measure_design(args, ops, flush, f"gpt2-style {size_name}", _gpt_like(sz, context), batch,
+                                           context, prompt_len))
+        out["rows"].append(_measure_design(args, ops, flush, f"fakilorn {size_name} heads 64/64 dense+experts",
+                                           FakilornConfig.from_dict(_fakilorn_raw(sz, 64, 64, True)), batch, context,
+                                           prompt_len))
+        mixed = (["gla", "attention", "mlstm", "gla"] * n)[:n]
+        for name, kinds, moe, loop in (("attention, dense", ["attention"] * n, False, False),
+                                       ("gla, dense", ["gla"] * n, False, False),
+                                       ("mlstm, dense", ["mlstm"] * n, False, False),
+                                       ("mixed, dense+experts" + (", loop" if n >= 3 else ""), mixed, True, n >= 3)):
+            cfg = ZenedraConfig.from_dict(_zenedra_raw(sz, kinds, moe, loop, context))
+            out["rows"].append(_measure_design(args, ops, flush, f"zenedra {size_name} {name}", cfg, batch, context,
+                                               prompt_len))
     return out
 
 
@@ -610,6 +679,8 @@ def run_ours(args) -> dict:
         return kernel_times(args)
     if args.only == "designs":
         return compare_designs(args)
+    if args.only == "zenedra":
+        return compare_zenedra(args)
     if args.only == "decode":
         cfg, windows, launches, mean_ctx, clocks = device_decode(args, args.batch, args.steps, args.warmup,
                                                                  min_seconds=0.0)

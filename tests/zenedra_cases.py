@@ -187,9 +187,14 @@ def relative_error(got: torch.Tensor, want: torch.Tensor) -> torch.Tensor:
     return (got.double().cpu() - want).abs().amax(-1) / want.std(-1)
 
 
-def assert_rows_close(got, want, tol, what: str, places=None) -> None:
+def assert_rows_close(got, want, tol, what: str, places=None, outliers: float = 0.0) -> None:
+    """``outliers``: the share of rows (at least one, if not zero) that may miss ``tol``, though not five times
+    ``tol``.  For bfloat16 runs: where a head's read-out nearly cancels (a query at right angles to the one key
+    its memory holds), the norm that follows magnifies the rounding of that one token by a hundred."""
     err = relative_error(got, want)
     bad = (~(err <= tol)).nonzero()
+    if outliers and 0 < bad.numel() <= max(1, int(outliers * err.numel())):
+        bad = (~(err <= 5 * tol)).nonzero()
     if bad.numel():
         i = int(bad[0])
         raise AssertionError(f"{what}: first wrong logits at {places[i] if places is not None else i}: "
