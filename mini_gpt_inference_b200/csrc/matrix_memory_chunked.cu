@@ -1,0 +1,373 @@
+// Mixers with a matrix memory per head (gated linear attention, mLSTM), prompt portions: the same
+// recurrence as the token-by-token scan of matrix_memory.cu, evaluated chunk by chunk so that all SMs
+// work and no step waits for the token before it.  A request's tokens of this step are cut into chunks
+// of L (the host lists them: request, first row, count); with b_t the sum of the logarithms of the decays
+// from the chunk's first token to t (per key channel for gated linear attention, one number per head for
+// the mLSTM), three kernels run:
+//
+//   1. per (chunk, head), all at once:  U = sum_j diag(exp(b_end - b_j)) k_j [v_j, 1]^T   (what the chunk
+//      adds to the state), and b itself for the other two kernels;
+//   2. per (request, head), chunk after chunk, element-wise:  S_prev(c) is stored where U(c) was, then
+//      S <- diag(exp(b_end)) S + U(c); the request's state slot is read at the start (unless the request
+//      is new) and written at the end;
+//   3. per (chunk, head), all at once:  o_t = (q_t * exp(b_t))^T S_prev + sum_{j <= t} A_tj v_j,
+//      A_tj = sum_d q_t[d] k_j[d] exp(b_t[d] - b_j[d]).
+//
+// Every exponent is <= 0: decays are only ever applied forward in time, so nothing overflows whatever the
+// decays are.  For the mLSTM the input gate i_j enters as exp(i_j) on k_j and everything is held relative to
+// the running maximum m of the sequential form (m_t = b_t + max(m_prev, max_{j <= t}(i_j - b_j)) inside a chunk;
+// a chunk's U is held relative to its own maximum and rescaled in kernel 2), and the normaliser is the
+// value column "1": n_t . q_t is that column's output and goes to `aux` with m_t, as in the sequential scan.
+// All sums, decays, exponentials and the state are 32-bit; only q, k and v arrive in the compute type.
+#include <math.h>
+
+#include "common.cuh"
+
+MG_GUARD_DECLARE(matrix_memory_chunked)
+
+namespace {
+
+constexpr int THREADS = 256;
+
+__device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
+
+struct ChunkParams {
+    const void* proj; int ld, q_off, k_off, v_off;
+    const float* gates; int gates_ld;
+    const int* chunks;            // [n_chunks, 4]: request, first row, tokens, unused
+    const int* req_chunks;        // [n_requests, 2]: first chunk, number of chunks
+    const int* req_ctx_before; const int* req_state_slot;
+    float* state; long long state_stride;
+    float* cum;                   // gla: [n_tokens, H, D] b_t;  mlstm: [n_tokens, H, 2] (b_t, i_t)
+    float* chunk_state;           // [n_chunks, H, DvE, D]: U, then S_prev
+    float* chunk_meta;            // mlstm: [n_chunks, H, 4]: b_end, the chunk's own maximum, m_prev
+    float* out; float* aux;
+    int n_chunks, n_requests, n_tokens, n_head, d, dv, L, n_slots;
+    float constant;
+};
+
+// ---- kernel 1 ----------------------------------------------------------------------------------------
+template <typename T, bool MLSTM>
+__global__ void __launch_bounds__(THREADS) chunk_local_kernel(const ChunkParams p) {
+    extern __shared__ __align__(16) float smem[];
+    const int D = p.d, DvE = p.dv + (MLSTM ? 1 : 0), DvP = (DvE + 7) / 8 * 8, L = p.L;
+    float* kt = smem;                           // [L][D + 1]
+    float* vs = kt + L * (D + 1);               // [L][DvP]
+    float* fc = vs + L * DvP;                   // mlstm: [L] b_j, then [L] i_j
+    __shared__ float b_end_s, own_max_s;
+    pdl_trigger();
+    pdl_wait();
+    const int c = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int row0 = p.chunks[4 * c + 1], count = p.chunks[4 * c + 2];
+    if (!MG_GUARDED(matrix_memory_chunked, MG_GUARD_ROW, row0 + count - 1, p.n_tokens) || count <= 0 || count > L) return;
+    const T* proj = reinterpret_cast<const T*>(p.proj);
+    if (!MLSTM) {
+        const float inv_tau = 1.0f / p.constant;
+        for (int d = tid; d < D; d += THREADS) {
+            float b = 0.f;
+            for (int j = 0; j < count; ++j) {
+                b += log_sigmoid(p.gates[(size_t)(row0 + j) * p.gates_ld + (size_t)h * D + d]) * inv_tau;
+                p.cum[((size_t)(row0 + j) * p.n_head + h) * D + d] = b;
+                kt[j * (D + 1) + d] = b;
+            }
+            for (int j = 0; j < L; ++j) {
+                float kv = 0.f;
+                if (j < count)
+                    kv = to_float(proj[(size_t)(row0 + j) * p.ld + p.k_off + (size_t)h * D + d]) * expf(b - kt[j * (D + 1) + d]);
+                kt[j * (D + 1) + d] = kv;
+            }
+        }
+    } else {
+        if (tid == 0) {
+            float b = 0.f, best = -INFINITY;
+            for (int j = 0; j < count; ++j) {
+                const float* g = p.gates + (size_t)(row0 + j) * p.gates_ld;
+                const float gi = p.constant * tanhf(g[h] / p.constant);
+                b += log_sigmoid(p.constant * tanhf(g[p.n_head + h] / p.constant));
+                fc[j] = b;
+                fc[L + j] = gi;
+                p.cum[((size_t)(row0 + j) * p.n_head + h) * 2] = b;
+                p.cum[((size_t)(row0 + j) * p.n_head + h) * 2 + 1] = gi;
+                best = fmaxf(best, gi - b);
+            }
+            b_end_s = b;
+            own_max_s = b + best;                               // the largest exponent of the chunk's own tokens at its end
+            p.chunk_meta[((size_t)c * p.n_head + h) * 4] = b;
+            p.chunk_meta[((size_t)c * p.n_head + h) * 4 + 1] = b + best;
+        }
+        __syncthreads();
+        for (int idx = tid; idx < L * D; idx += THREADS) {
+            const int j = idx / D, d = idx - j * D;
+            float kv = 0.f;
+            if (j < count)
+                kv = to_float(proj[(size_t)(row0 + j) * p.ld + p.k_off + (size_t)h * D + d]) *
+                     expf(b_end_s - fc[j] + fc[L + j] - own_max_s);
+            kt[j * (D + 1) + d] = kv;
+        }
+    }
+    for (int idx = tid; idx < L * DvP; idx += THREADS) {
+        const int j = idx / DvP, e = idx - j * DvP;
+        float vv = 0.f;
+        if (j < count) {
+            if (e < p.dv) vv = to_float(proj[(size_t)(row0 + j) * p.ld + p.v_off + (size_t)h * p.dv + e]);
+            else if (MLSTM && e == p.dv) vv = 1.f;
+        }
+        vs[idx] = vv;
+    }
+    __syncthreads();
+    float* U = p.chunk_state + ((size_t)c * p.n_head + h) * DvE * D;
+    const int items = (DvP / 8) * D;
+    for (int item = tid; item < items; item += THREADS) {
+        const int e0 = (item / D) * 8, d = item - (item / D) * D;
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int j = 0; j < count; ++j) {
+            const float kv = kt[j * (D + 1) + d];
+            const float4 v0 = *reinterpret_cast<const float4*>(&vs[j * DvP + e0]);
+            const float4 v1 = *reinterpret_cast<const float4*>(&vs[j * DvP + e0 + 4]);
+            acc[0] = fmaf(kv, v0.x, acc[0]); acc[1] = fmaf(kv, v0.y, acc[1]);
+            acc[2] = fmaf(kv, v0.z, acc[2]); acc[3] = fmaf(kv, v0.w, acc[3]);
+            acc[4] = fmaf(kv, v1.x, acc[4]); acc[5] = fmaf(kv, v1.y, acc[5]);
+            acc[6] = fmaf(kv, v1.z, acc[6]); acc[7] = fmaf(kv, v1.w, acc[7]);
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            if (e0 + u < DvE) U[(size_t)(e0 + u) * D + d] = acc[u];
+    }
+}
+
+// ---- kernel 2 ----------------------------------------------------------------------------------------
+template <bool MLSTM>
+__global__ void __launch_bounds__(THREADS) chunk_scan_kernel(const ChunkParams p) {
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.z, h = blockIdx.y;
+    const int D = p.d, DvE = p.dv + (MLSTM ? 1 : 0);
+    const int idx = blockIdx.x * THREADS + threadIdx.x;              // element (e, d) of the head's state
+    const int first = p.req_chunks[2 * r], n = p.req_chunks[2 * r + 1];
+    if (n <= 0) return;
+    int slot = p.req_state_slot[r];
+    if (!MG_GUARDED(matrix_memory_chunked, MG_GUARD_ROW, slot, p.n_slots) ||
+        !MG_GUARDED(matrix_memory_chunked, MG_GUARD_ROW, first + n - 1, p.n_chunks))
+        return;
+    const bool fresh = p.req_ctx_before[r] == 0;
+    const bool mine = idx < DvE * D;
+    const int d = mine ? idx % D : 0;
+    float* slot_base = p.state + (size_t)slot * p.state_stride;
+    float* s_ptr = slot_base + (size_t)h * DvE * D + (mine ? idx : 0);
+    float* m_ptr = slot_base + (size_t)p.n_head * DvE * D + h;
+    float S = (mine && !fresh) ? *s_ptr : 0.f;
+    float m = (MLSTM && !fresh) ? *m_ptr : 0.f;
+    for (int c0 = first; c0 < first + n; c0 += 4) {
+        float U[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)                                     // four chunks' loads in flight at once
+            U[u] = (mine && c0 + u < first + n) ? p.chunk_state[((size_t)(c0 + u) * p.n_head + h) * DvE * D + idx] : 0.f;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int c = c0 + u;
+            if (c >= first + n) break;
+            if (mine) p.chunk_state[((size_t)c * p.n_head + h) * DvE * D + idx] = S;
+            if (MLSTM) {
+                float* meta = p.chunk_meta + ((size_t)c * p.n_head + h) * 4;
+                const float b_end = meta[0], own = meta[1];
+                const float m_end = fmaxf(b_end + m, own);
+                if (blockIdx.x == 0 && threadIdx.x == 0) meta[2] = m;
+                S = expf(b_end + m - m_end) * S + expf(own - m_end) * U[u];
+                m = m_end;
+            } else {
+                const int last = p.chunks[4 * c + 1] + p.chunks[4 * c + 2] - 1;
+                S = fmaf(expf(p.cum[((size_t)last * p.n_head + h) * D + d]), S, U[u]);
+            }
+        }
+    }
+    if (mine) *s_ptr = S;
+    if (MLSTM && blockIdx.x == 0 && threadIdx.x == 0) *m_ptr = m;
+}
+
+// ---- kernel 3 ----------------------------------------------------------------------------------------
+template <typename T, bool MLSTM>
+__global__ void __launch_bounds__(THREADS) chunk_output_kernel(const ChunkParams p) {
+    extern __shared__ __align__(16) float smem[];
+    const int D = p.d, Dv = p.dv, DvE = Dv + (MLSTM ? 1 : 0), L = p.L;
+    const int SP = DvE + 1;                                          // stride of the staged state: odd, conflict-free
+    float* qs = smem;                           // [L][D + 1]
+    float* ks = qs + L * (D + 1);               // [L][D + 1]
+    float* bs = ks + L * (D + 1);               // gla: [L][D + 1];  mlstm: [3 L]: b, i, m
+    float* vs = bs + (MLSTM ? 3 * L : L * (D + 1));   // [L][Dv]
+    float* As = vs + L * Dv;                    // [L][L + 1]
+    float* Ss = As + L * (L + 1);               // [D][SP]: the state before the chunk, transposed
+    pdl_trigger();
+    pdl_wait();
+    const int c = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int row0 = p.chunks[4 * c + 1], count = p.chunks[4 * c + 2];
+    if (!MG_GUARDED(matrix_memory_chunked, MG_GUARD_ROW, row0 + count - 1, p.n_tokens) || count <= 0 || count > L) return;
+    const T* proj = reinterpret_cast<const T*>(p.proj);
+    const float q_scale = 1.0f / sqrtf((float)D);
+    for (int idx = tid; idx < L * D; idx += THREADS) {
+        const int j = idx / D, d = idx - j * D;
+        float qv = 0.f, kv = 0.f, bv = 0.f;
+        if (j < count) {
+            const T* row = proj + (size_t)(row0 + j) * p.ld + (size_t)h * D + d;
+            qv = to_float(row[p.q_off]) * q_scale;
+            kv = to_float(row[p.k_off]);
+            if (!MLSTM) bv = p.cum[((size_t)(row0 + j) * p.n_head + h) * D + d];
+        }
+        qs[j * (D + 1) + d] = qv;
+        ks[j * (D + 1) + d] = kv;
+        if (!MLSTM) bs[j * (D + 1) + d] = bv;
+    }
+    for (int idx = tid; idx < L * Dv; idx += THREADS) {
+        const int j = idx / Dv, e = idx - j * Dv;
+        vs[idx] = j < count ? to_float(proj[(size_t)(row0 + j) * p.ld + p.v_off + (size_t)h * Dv + e]) : 0.f;
+    }
+    const float* S_prev = p.chunk_state + ((size_t)c * p.n_head + h) * DvE * D;
+    for (int idx = tid; idx < DvE * D; idx += THREADS) {
+        const int e = idx / D, d = idx - e * D;
+        Ss[d * SP + e] = S_prev[idx];
+    }
+    float m_prev = 0.f;
+    if (MLSTM) {
+        m_prev = p.chunk_meta[((size_t)c * p.n_head + h) * 4 + 2];
+        if (tid == 0) {
+            float best = -INFINITY;
+            for (int j = 0; j < L; ++j) {
+                float b = 0.f, gi = 0.f;
+                if (j < count) {
+                    b = p.cum[((size_t)(row0 + j) * p.n_head + h) * 2];
+                    gi = p.cum[((size_t)(row0 + j) * p.n_head + h) * 2 + 1];
+                    best = fmaxf(best, gi - b);
+                }
+                bs[j] = b;
+                bs[L + j] = gi;
+                bs[2 * L + j] = b + fmaxf(m_prev, best);            // m_t
+            }
+        }
+    }
+    __syncthreads();
+    // scores of the chunk's own tokens
+    for (int idx = tid; idx < L * L; idx += THREADS) {
+        const int t = idx / L, j = idx - t * L;
+        float a = 0.f;
+        if (j <= t && t < count) {
+            const float* qr = qs + t * (D + 1);
+            const float* kr = ks + j * (D + 1);
+            if (MLSTM) {
+                for (int d = 0; d < D; ++d) a = fmaf(qr[d], kr[d], a);
+                a *= __expf(bs[t] - bs[j] + bs[L + j] - bs[2 * L + t]);
+            } else {
+                const float* bt = bs + t * (D + 1);
+                const float* bj = bs + j * (D + 1);
+                for (int d = 0; d < D; ++d) a = fmaf(qr[d] * kr[d], __expf(bt[d] - bj[d]), a);
+            }
+        }
+        As[t * (L + 1) + j] = a;
+    }
+    __syncthreads();
+    // the queries as the state before the chunk sees them
+    for (int idx = tid; idx < L * D; idx += THREADS) {
+        const int t = idx / D, d = idx - t * D;
+        const float f = MLSTM ? __expf(bs[t] + m_prev - bs[2 * L + t]) : __expf(bs[t * (D + 1) + d]);
+        qs[t * (D + 1) + d] *= f;
+    }
+    __syncthreads();
+    // o[t][e]: four rows and one column a thread
+    const int items = (L / 4) * Dv;
+    for (int item = tid; item < items; item += THREADS) {
+        const int e = item % Dv, t0 = (item / Dv) * 4;
+        if (t0 >= count) continue;
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int j = 0; j <= t0 + 3 && j < count; ++j) {
+            const float vv = vs[j * Dv + e];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) acc[u] = fmaf(As[(t0 + u) * (L + 1) + j], vv, acc[u]);
+        }
+        for (int d = 0; d < D; ++d) {
+            const float sv = Ss[d * SP + e];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) acc[u] = fmaf(qs[(t0 + u) * (D + 1) + d], sv, acc[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (t0 + u < count) p.out[((size_t)(row0 + t0 + u) * p.n_head + h) * Dv + e] = acc[u];
+    }
+    if (MLSTM && tid < count) {                                       // the normaliser's column, a row a thread
+        const int t = tid;
+        float nq = 0.f;
+        for (int j = 0; j <= t; ++j) nq += As[t * (L + 1) + j];
+        for (int d = 0; d < D; ++d) nq = fmaf(qs[t * (D + 1) + d], Ss[d * SP + Dv], nq);
+        p.aux[((size_t)(row0 + t) * p.n_head + h) * 2] = nq;
+        p.aux[((size_t)(row0 + t) * p.n_head + h) * 2 + 1] = bs[2 * L + t];
+    }
+}
+
+size_t local_smem(int L, int D, int DvE, bool mlstm) {
+    return sizeof(float) * ((size_t)L * (D + 1) + (size_t)L * ((DvE + 7) / 8 * 8) + (mlstm ? 2 * L : 0));
+}
+size_t output_smem(int L, int D, int Dv, bool mlstm) {
+    const int DvE = Dv + (mlstm ? 1 : 0);
+    return sizeof(float) * ((size_t)2 * L * (D + 1) + (mlstm ? 3 * L : (size_t)L * (D + 1)) + (size_t)L * Dv +
+                            (size_t)L * (L + 1) + (size_t)D * (DvE + 1));
+}
+constexpr size_t SMEM_LIMIT = 200 * 1024;
+
+template <typename T, bool MLSTM>
+int run_chunked(const ChunkParams& p, cudaStream_t s) {
+    const int DvE = p.dv + (MLSTM ? 1 : 0);
+    const size_t s1 = local_smem(p.L, p.d, DvE, MLSTM), s3 = output_smem(p.L, p.d, p.dv, MLSTM);
+    cudaError_t e = cudaFuncSetAttribute(chunk_local_kernel<T, MLSTM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(chunk_output_kernel<T, MLSTM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT);
+    if (e != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "matrix memory (chunks): %s", cudaGetErrorString(e));
+    e = mg_launch(chunk_local_kernel<T, MLSTM>, dim3(p.n_chunks, p.n_head), dim3(THREADS), s1, s, true, p);
+    if (e == cudaSuccess)
+        e = mg_launch(chunk_scan_kernel<MLSTM>, dim3(ceil_div(DvE * p.d, THREADS), p.n_head, p.n_requests), dim3(THREADS), 0, s, true, p);
+    if (e == cudaSuccess)
+        e = mg_launch(chunk_output_kernel<T, MLSTM>, dim3(p.n_chunks, p.n_head), dim3(THREADS), s3, s, true, p);
+    if (e != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "matrix memory (chunks): %s", cudaGetErrorString(e));
+    return MG_OK;
+}
+
+}  // namespace
+
+// The longest chunk (64 or 32 tokens) whose tiles fit the shared memory of an SM for heads of these sizes;
+// 0 if none does (then the sequential scan serves).
+MG_API int mg_matrix_memory_chunk_tokens(int head_dim, int v_dim, int mlstm) {
+    for (int L = 64; L >= 32; L /= 2)
+        if (output_smem(L, head_dim, v_dim, mlstm != 0) <= SMEM_LIMIT && local_smem(L, head_dim, v_dim + 1, mlstm != 0) <= SMEM_LIMIT)
+            return L;
+    return 0;
+}
+
+// As mg_matrix_memory_scan (same rows, gates, state slots, out and aux), for steps with prompt portions.
+// chunks: [n_chunks, 4] (request, first row, tokens <= chunk_tokens, unused) in row order; req_chunks:
+// [n_requests, 2] (first chunk, chunks); cum: [n_tokens, n_head, mlstm ? 2 : head_dim] floats; chunk_state:
+// [n_chunks, n_head, v_dim + mlstm, head_dim] floats; chunk_meta: [n_chunks, n_head, 4] floats (mlstm; else null).
+MG_API int mg_matrix_memory_chunked(const void* proj, int ld, int q_off, int k_off, int v_off, const float* gates,
+                                    int gates_ld, const int* chunks, const int* req_chunks, const int* req_ctx_before,
+                                    const int* req_state_slot, float* state, long long state_stride, float* cum,
+                                    float* chunk_state, float* chunk_meta, float* out, float* aux, int n_chunks,
+                                    int chunk_tokens, int n_requests, int n_tokens, int n_head, int head_dim, int v_dim,
+                                    float constant, int mlstm, int n_slots, int is_bf16, void* stream) {
+    if (n_requests == 0 || n_tokens == 0 || n_chunks == 0) return MG_OK;
+    MG_REQUIRE(n_requests > 0 && n_tokens > 0 && n_chunks > 0 && n_head > 0 && head_dim > 0 && v_dim > 0 && n_slots > 0,
+               "matrix memory (chunks): bad sizes");
+    MG_REQUIRE(n_head <= 65535 && n_requests <= 65535, "matrix memory (chunks): too many heads or requests");
+    MG_REQUIRE(constant > 0.f, "matrix memory (chunks): tau and the gates' cap must be positive");
+    const int cols = v_dim + (mlstm ? 1 : 0);
+    MG_REQUIRE(state_stride >= (long long)n_head * cols * head_dim + (mlstm ? n_head : 0), "matrix memory (chunks): the state slots are too small");
+    MG_REQUIRE(q_off >= 0 && k_off >= 0 && v_off >= 0 && q_off + n_head * head_dim <= ld && k_off + n_head * head_dim <= ld &&
+                   v_off + n_head * v_dim <= ld, "matrix memory (chunks): heads outside the rows");
+    MG_REQUIRE(gates_ld >= (mlstm ? 2 * n_head : n_head * head_dim), "matrix memory (chunks): the gates' rows are too short");
+    MG_REQUIRE(cum && chunk_state && (!mlstm || (chunk_meta && aux)), "matrix memory (chunks): scratch is missing");
+    MG_REQUIRE((chunk_tokens == 32 || chunk_tokens == 64) && chunk_tokens <= mg_matrix_memory_chunk_tokens(head_dim, v_dim, mlstm),
+               "matrix memory (chunks): chunks of %d tokens do not fit heads of %d and %d", chunk_tokens, head_dim, v_dim);
+    ChunkParams p;
+    p.proj = proj; p.ld = ld; p.q_off = q_off; p.k_off = k_off; p.v_off = v_off; p.gates = gates; p.gates_ld = gates_ld;
+    p.chunks = chunks; p.req_chunks = req_chunks; p.req_ctx_before = req_ctx_before; p.req_state_slot = req_state_slot;
+    p.state = state; p.state_stride = state_stride; p.cum = cum; p.chunk_state = chunk_state; p.chunk_meta = chunk_meta;
+    p.out = out; p.aux = aux; p.n_chunks = n_chunks; p.n_requests = n_requests; p.n_tokens = n_tokens; p.n_head = n_head;
+    p.d = head_dim; p.dv = v_dim; p.L = chunk_tokens; p.n_slots = n_slots; p.constant = constant;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (is_bf16) return mlstm ? run_chunked<bf16, true>(p, s) : run_chunked<bf16, false>(p, s);
+    return mlstm ? run_chunked<float, true>(p, s) : run_chunked<float, false>(p, s);
+}

@@ -32,6 +32,9 @@ _SIGNATURES = {
     "mg_concat_cast": [_P, _P, _P, _I, _I, _I, _P],
     "mg_matrix_memory_scan": [_P, _I, _I, _I, _I, _P, _I, _P, _P, _P, _P, _P, ctypes.c_longlong, _P, _P, _I, _I, _I, _I,
                               _I, _F, _I, _I, _I, _P],
+    "mg_matrix_memory_chunked": [_P, _I, _I, _I, _I, _P, _I, _P, _P, _P, _P, _P, ctypes.c_longlong, _P, _P, _P, _P, _P, _I,
+                                 _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
+    "mg_matrix_memory_chunk_tokens": [_I, _I, _I],
     "mg_head_norm_gate": [_P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _F, _I, _I, _I, _P],
     "mg_moe_route_scored": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "mg_attention_mma": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F,
@@ -76,7 +79,7 @@ _SIGNATURES = {
 
 # exported readers of the kernel files' index guards: mg_<name>_index_fault(long long[4])
 GUARDED_FILES = ("elementwise", "linear_skinny", "linear_stream", "linear_wide", "linear_cluster", "linear_tc",
-                 "attention_generic", "attention_split", "attention_prefill", "head_prepare", "moe", "attention_mma", "matrix_memory")
+                 "attention_generic", "attention_split", "attention_prefill", "head_prepare", "moe", "attention_mma", "matrix_memory", "matrix_memory_chunked")
 for _name in GUARDED_FILES:
     _SIGNATURES[f"mg_{_name}_index_fault"] = [_P]
 GUARD_CODES = {1: "token id", 2: "position", 3: "cache row", 4: "page", 5: "request", 6: "row", 7: "token source"}

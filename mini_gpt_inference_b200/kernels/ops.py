@@ -95,6 +95,7 @@ class CudaOps:
         self.use_dependent_launch = True
         self.use_prefill_tc = True
         self.use_mma_attention = True
+        self.use_chunked_memory = True     # prompt portions of the matrix-memory mixers chunk by chunk (bfloat16)
         self.merge_ranges_in_last_cta = False
         self._counter_buf = None
         self._retired_counters = []
@@ -313,6 +314,36 @@ class CudaOps:
         return out
 
     # ---- mixers with a matrix memory ------------------------------------------------------------------
+    MEMORY_CHUNK_MIN_TOKENS = 32     # a step whose longest portion is shorter runs the token-by-token scan
+
+    def _memory_chunks_name(self, head_dim, v_dim, mlstm):
+        tokens = self.lib.mg_matrix_memory_chunk_tokens(int(head_dim), int(v_dim), 1 if mlstm else 0)
+        return (f"memory_chunks/{tokens}", tokens) if tokens > 0 else (None, 0)
+
+    def plan_memory_chunks(self, batch, plan, head_dim, v_dim, mlstm) -> None:
+        """Host half of the chunked scan of the matrix-memory mixers: the step's tokens cut into chunks, request
+        by request (``[chunks, 4]``: request, first row, tokens, 0) and each request's range of chunks
+        (``[requests, 2]``), under a name that layers with the same chunk length share.  Nothing is planned
+        for 32-bit steps (the token-by-token scan has one fixed order of sums whatever the cut) and for steps
+        of short portions."""
+        if (not self.use_chunked_memory or batch.act_dtype != torch.bfloat16
+                or max(batch.q_len) < self.MEMORY_CHUNK_MIN_TOKENS):
+            return
+        name, tokens = self._memory_chunks_name(head_dim, v_dim, mlstm)
+        if name is None or name in plan.arrays:
+            return
+        import numpy as np
+
+        chunks, ranges, row = [], [], 0
+        for r, n in enumerate(batch.q_len):
+            ranges.append((len(chunks), -(-n // tokens)))
+            for first in range(0, n, tokens):
+                chunks.append((r, row + first, min(tokens, n - first), 0))
+            row += n
+        plan.arrays[name] = np.asarray(chunks, dtype=np.int32).reshape(-1, 4)
+        plan.arrays[name + "/requests"] = np.asarray(ranges, dtype=np.int32).reshape(-1, 2)
+        plan.signature.append(("memory_chunks", tokens))
+
     def matrix_memory_scan(self, ctx, mode, proj, q_off, k_off, v_off, n_head, head_dim, v_dim, gates, constant, state):
         """The scan of a mixer with a matrix memory over the step's tokens, request by request, from and to
         the requests' state slots.  ``mode`` ``"gla"``: ``gates`` are the decays' pre-activations
@@ -331,6 +362,23 @@ class CudaOps:
         mlstm = mode == "mlstm"
         out = torch.empty((n, n_head * v_dim), dtype=torch.float32, device=self.device)
         aux = torch.empty((n, n_head, 2), dtype=torch.float32, device=self.device) if mlstm else None
+        name, tokens = self._memory_chunks_name(head_dim, v_dim, mlstm)
+        chunks = getattr(ctx, "extra", {}).get(name) if name is not None else None
+        if chunks is not None and chunks.shape[0] > 0 and self.use_chunked_memory:
+            # a step with prompt portions: chunk by chunk (three kernels, every SM at work)
+            ranges = ctx.extra[name + "/requests"]
+            cols = v_dim + (1 if mlstm else 0)
+            cum = torch.empty((n, n_head, 2 if mlstm else head_dim), dtype=torch.float32, device=self.device)
+            chunk_state = torch.empty((chunks.shape[0], n_head, cols, head_dim), dtype=torch.float32, device=self.device)
+            meta = torch.empty((chunks.shape[0], n_head, 4), dtype=torch.float32, device=self.device) if mlstm else None
+            self._run(self.lib.mg_matrix_memory_chunked(
+                _ptr(proj), proj.shape[1], q_off, k_off, v_off, _ptr(gates), gates.shape[1], _ptr(chunks), _ptr(ranges),
+                _ptr(ctx.req_ctx_before), _ptr(ctx.req_state_slot), _ptr(state), state.shape[1], _ptr(cum),
+                _ptr(chunk_state), _ptr(meta), _ptr(out), _ptr(aux), chunks.shape[0], tokens, ranges.shape[0], n, n_head,
+                head_dim, v_dim, float(constant), 1 if mlstm else 0, state.shape[0], self._is_bf16(proj), self._stream()),
+                "matrix memory (chunks)")
+            self.launches += 2
+            return out, aux
         self._run(self.lib.mg_matrix_memory_scan(
             _ptr(proj), proj.shape[1], q_off, k_off, v_off, _ptr(gates), gates.shape[1], _ptr(ctx.req_q_start),
             _ptr(ctx.req_q_len), _ptr(ctx.req_ctx_before), _ptr(ctx.req_state_slot), _ptr(state), state.shape[1], _ptr(out),

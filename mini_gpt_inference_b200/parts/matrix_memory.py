@@ -63,6 +63,12 @@ class _MatrixMemoryMixer(Mixer):
         self.norm_gain = tensors.get(p + "norm")
         return True
 
+    def plan_step(self, batch, plan, ops) -> None:
+        # the kernel set may cut prompt portions into chunks that it scans side by side
+        planner = getattr(ops, "plan_memory_chunks", None)
+        if planner is not None:
+            planner(batch, plan, self.head_dim, self.v_head_dim, self.mode == "mlstm")
+
     def _finish(self, ctx, proj, memory_out, aux, residual32, per_head_gain: bool, gate_activation: str):
         gate = proj[:, self.g_off: self.g_off + self.v_width]
         heads = ctx.ops.head_norm_gate(memory_out, aux, gate, self.norm_gain, self.n_head, self.v_head_dim,

@@ -167,6 +167,62 @@ def test_matrix_memory_prompt_portions_and_single_tokens(ops, dtype, mode, heads
             close(g, x, dtype, f"{mode} cut as {cuts[0][:3]}", 4.0 if dtype == "bfloat16" else 3.0)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("mode,strong", [("gla", False), ("gla", True), ("mlstm", False), ("mlstm", True)])
+@pytest.mark.parametrize("heads,d,dv", [(2, 24, 40), (1, 8, 33), (2, 64, 128), (1, 128, 200), (1, 200, 16)])
+def test_matrix_memory_chunk_by_chunk(ops, dtype, mode, strong, heads, d, dv):
+    """The chunked form that serves prompt portions, against the plain mixer: three requests of unequal
+    lengths in one step (chunks that are full, partial and of one token), then a second step that goes on
+    from the state slots the first one left; the work list is made by the kernel set's own planner.  The
+    kernels take 32-bit rows too (the engine gives them bfloat16 steps only), which is the sharp comparison.
+    ``strong``: decays and gates so strong that a chunk's first token is forgotten many times over by its
+    end, which must not overflow anything."""
+    t, c, eps = DTYPES[dtype], 48, 1e-4
+    gen = torch.Generator().manual_seed(d + dv + heads)
+    m = {"heads": heads, "dim": d, "vdim": dv, "tau": 0.5 if strong else 6.0, "gate_cap": 40.0 if strong else 8.0}
+    w = _memory_weights(gen, mode, c, heads, d, dv)
+    if strong and mode == "gla":
+        w["a2.b"] = w["a2.b"] - 6.0
+    if strong and mode == "mlstm":
+        w["i"], w["f"], w["f.b"] = w["i"] * 40.0, w["f"] * 20.0, w["f.b"] - 10.0
+    if dtype == "bfloat16":
+        w = {k: v.to(torch.bfloat16).float() for k, v in w.items()}
+    wd = {k: v.double() for k, v in w.items()}
+    h = [torch.randn(n, c, generator=gen) for n in (150, 70, 33)]
+    mixer = plain.gla_mixer if mode == "gla" else plain.mlstm_mixer
+    want = [mixer(x.double(), wd, "", m, eps) for x in h]
+    cols = dv + (1 if mode == "mlstm" else 0)
+    state = torch.full((5, heads * cols * d + heads), float("nan"), device="cuda:0")
+    got = [[], [], []]
+    for portions, before in (([100, 70, 5], [0, 0, 0]), ([50, 0, 28], [100, 70, 5])):
+        live = [r for r in range(3) if portions[r]]
+        x = torch.cat([h[r][before[r]: before[r] + portions[r]] for r in live]).double()
+        proj = dev(torch.cat([x @ wd[k].T for k in ("q", "k", "v", "g")], dim=1), t)
+        if mode == "gla":
+            gates, const = (x @ wd["a1"].T) @ wd["a2"].T + wd["a2.b"], m["tau"]
+        else:
+            gates, const = torch.cat([x @ wd["i"].T + wd["i.b"], x @ wd["f"].T + wd["f.b"]], dim=1), m["gate_cap"]
+        ctx = batch([portions[r] for r in live], [before[r] for r in live], [[3, 0, 4][r] for r in live])
+        plan = SimpleNamespace(arrays={}, signature=[])
+        ops.plan_memory_chunks(SimpleNamespace(q_len=[portions[r] for r in live], act_dtype=torch.bfloat16), plan, d, dv,
+                               mode == "mlstm")
+        assert len(plan.arrays) == 2 and plan.signature
+        ctx.extra = {k: dev(torch.from_numpy(v)) for k, v in plan.arrays.items()}
+        launches = ops.launches
+        o, aux = ops.matrix_memory_scan(ctx, mode, proj, 0, heads * d, 2 * heads * d, heads, d, dv, dev(gates.float()),
+                                        const, state)
+        assert ops.launches == launches + 3                       # the three kernels of the chunked form ran
+        y = ops.head_norm_gate(o, aux, proj[:, 2 * heads * d + heads * dv:], dev(w["norm"]), heads, dv, eps,
+                               mode == "mlstm", "sigmoid" if mode == "mlstm" else "silu", t, positions=ctx.positions)
+        y = y.double().cpu() @ wd["o"].T
+        row = 0
+        for r in live:
+            got[r].append(y[row: row + portions[r]])
+            row += portions[r]
+    for r in range(3):
+        close(torch.cat(got[r]), want[r], dtype, f"{mode} chunk by chunk, request {r}", 5.0)
+
+
 def test_matrix_memory_keeps_a_far_token(ops):
     """Decays close to one: after 600 tokens the read-out still leans on token 3, whose key the last query
     repeats, thirty times as long as any other.  A state that is reset, cut off or decayed wrongly loses it."""
