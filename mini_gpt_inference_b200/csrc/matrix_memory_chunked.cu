@@ -53,7 +53,7 @@ __global__ void __launch_bounds__(THREADS) chunk_local_kernel(const ChunkParams 
     const int D = p.d, DvE = p.dv + (MLSTM ? 1 : 0), DvP = (DvE + 7) / 8 * 8, L = p.L;
     float* kt = smem;                           // [L][D + 1]
     float* vs = kt + L * (D + 1);               // [L][DvP]
-    float* fc = vs + L * DvP;                   // mlstm: [L] b_j, then [L] i_j
+    float* fc = vs + L * DvP;                   // mlstm: [L] b_j, then [L] i_j;  gla: [L][D + 1] b_j
     __shared__ float b_end_s, own_max_s;
     pdl_trigger();
     pdl_wait();
@@ -62,33 +62,50 @@ __global__ void __launch_bounds__(THREADS) chunk_local_kernel(const ChunkParams 
     if (!MG_GUARDED(matrix_memory_chunked, MG_GUARD_ROW, row0 + count - 1, p.n_tokens) || count <= 0 || count > L) return;
     const T* proj = reinterpret_cast<const T*>(p.proj);
     if (!MLSTM) {
+        // the logarithms of the decays, all at once; then their running sums, a thread per key channel; then the
+        // keys as the chunk's end sees them, all at once again
         const float inv_tau = 1.0f / p.constant;
+        for (int idx = tid; idx < L * D; idx += THREADS) {
+            const int j = idx / D, d = idx - j * D;
+            fc[j * (D + 1) + d] = j < count ? log_sigmoid(p.gates[(size_t)(row0 + j) * p.gates_ld + (size_t)h * D + d]) * inv_tau : 0.f;
+        }
+        __syncthreads();
         for (int d = tid; d < D; d += THREADS) {
             float b = 0.f;
-            for (int j = 0; j < count; ++j) {
-                b += log_sigmoid(p.gates[(size_t)(row0 + j) * p.gates_ld + (size_t)h * D + d]) * inv_tau;
-                p.cum[((size_t)(row0 + j) * p.n_head + h) * D + d] = b;
-                kt[j * (D + 1) + d] = b;
-            }
             for (int j = 0; j < L; ++j) {
-                float kv = 0.f;
-                if (j < count)
-                    kv = to_float(proj[(size_t)(row0 + j) * p.ld + p.k_off + (size_t)h * D + d]) * expf(b - kt[j * (D + 1) + d]);
-                kt[j * (D + 1) + d] = kv;
+                b += fc[j * (D + 1) + d];
+                fc[j * (D + 1) + d] = b;
             }
         }
+        __syncthreads();
+        for (int idx = tid; idx < L * D; idx += THREADS) {
+            const int j = idx / D, d = idx - j * D;
+            const float b = fc[j * (D + 1) + d], b_end = fc[(L - 1) * (D + 1) + d];
+            float kv = 0.f;
+            if (j < count) {
+                p.cum[((size_t)(row0 + j) * p.n_head + h) * D + d] = b;
+                kv = to_float(proj[(size_t)(row0 + j) * p.ld + p.k_off + (size_t)h * D + d]) * expf(b_end - b);
+            }
+            kt[j * (D + 1) + d] = kv;
+        }
     } else {
+        if (tid < L) {                                          // the two gates of every token, all at once
+            float gi = 0.f, lf = 0.f;
+            if (tid < count) {
+                const float* g = p.gates + (size_t)(row0 + tid) * p.gates_ld;
+                gi = p.constant * tanhf(g[h] / p.constant);
+                lf = log_sigmoid(p.constant * tanhf(g[p.n_head + h] / p.constant));
+            }
+            fc[tid] = lf;
+            fc[L + tid] = gi;
+        }
+        __syncthreads();
         if (tid == 0) {
             float b = 0.f, best = -INFINITY;
             for (int j = 0; j < count; ++j) {
-                const float* g = p.gates + (size_t)(row0 + j) * p.gates_ld;
-                const float gi = p.constant * tanhf(g[h] / p.constant);
-                b += log_sigmoid(p.constant * tanhf(g[p.n_head + h] / p.constant));
+                b += fc[j];
                 fc[j] = b;
-                fc[L + j] = gi;
-                p.cum[((size_t)(row0 + j) * p.n_head + h) * 2] = b;
-                p.cum[((size_t)(row0 + j) * p.n_head + h) * 2 + 1] = gi;
-                best = fmaxf(best, gi - b);
+                best = fmaxf(best, fc[L + j] - b);
             }
             b_end_s = b;
             own_max_s = b + best;                               // the largest exponent of the chunk's own tokens at its end
@@ -96,6 +113,10 @@ __global__ void __launch_bounds__(THREADS) chunk_local_kernel(const ChunkParams 
             p.chunk_meta[((size_t)c * p.n_head + h) * 4 + 1] = b + best;
         }
         __syncthreads();
+        if (tid < count) {
+            p.cum[((size_t)(row0 + tid) * p.n_head + h) * 2] = fc[tid];
+            p.cum[((size_t)(row0 + tid) * p.n_head + h) * 2 + 1] = fc[L + tid];
+        }
         for (int idx = tid; idx < L * D; idx += THREADS) {
             const int j = idx / D, d = idx - j * D;
             float kv = 0.f;
@@ -228,27 +249,30 @@ __global__ void __launch_bounds__(THREADS) chunk_output_kernel(const ChunkParams
     float m_prev = 0.f;
     if (MLSTM) {
         m_prev = p.chunk_meta[((size_t)c * p.n_head + h) * 4 + 2];
+        if (tid < L) {
+            bs[tid] = tid < count ? p.cum[((size_t)(row0 + tid) * p.n_head + h) * 2] : 0.f;
+            bs[L + tid] = tid < count ? p.cum[((size_t)(row0 + tid) * p.n_head + h) * 2 + 1] : 0.f;
+        }
+        __syncthreads();
         if (tid == 0) {
             float best = -INFINITY;
             for (int j = 0; j < L; ++j) {
-                float b = 0.f, gi = 0.f;
-                if (j < count) {
-                    b = p.cum[((size_t)(row0 + j) * p.n_head + h) * 2];
-                    gi = p.cum[((size_t)(row0 + j) * p.n_head + h) * 2 + 1];
-                    best = fmaxf(best, gi - b);
-                }
-                bs[j] = b;
-                bs[L + j] = gi;
-                bs[2 * L + j] = b + fmaxf(m_prev, best);            // m_t
+                if (j < count) best = fmaxf(best, bs[L + j] - bs[j]);
+                bs[2 * L + j] = bs[j] + fmaxf(m_prev, best);        // m_t
             }
         }
     }
     __syncthreads();
     // scores of the chunk's own tokens
-    for (int idx = tid; idx < L * L; idx += THREADS) {
-        const int t = idx / L, j = idx - t * L;
+    for (int idx = tid; idx < L * (L + 1); idx += THREADS) As[idx] = 0.f;
+    __syncthreads();
+    // (rows t and L - 1 - t have L + 1 visible keys between them: a pair of rows is one run of L + 1 entries)
+    for (int idx = tid; idx < (L / 2) * (L + 1); idx += THREADS) {
+        const int pair = idx / (L + 1), k = idx - pair * (L + 1);
+        const int t = k <= pair ? pair : L - 1 - pair, j = k <= pair ? k : k - pair - 1;
+        if (t >= count) continue;
         float a = 0.f;
-        if (j <= t && t < count) {
+        {
             const float* qr = qs + t * (D + 1);
             const float* kr = ks + j * (D + 1);
             if (MLSTM) {
@@ -270,25 +294,47 @@ __global__ void __launch_bounds__(THREADS) chunk_output_kernel(const ChunkParams
         qs[t * (D + 1) + d] *= f;
     }
     __syncthreads();
-    // o[t][e]: four rows and one column a thread
-    const int items = (L / 4) * Dv;
-    for (int item = tid; item < items; item += THREADS) {
-        const int e = item % Dv, t0 = (item / Dv) * 4;
+    // o[t][e]: a warp takes four rows and 128 columns at a time, a lane four of the columns (32 apart)
+    const int warp = tid >> 5, lane = tid & 31;
+    const int col_groups = (Dv + 127) / 128;
+    for (int item = warp; item < (L / 4) * col_groups; item += THREADS / 32) {
+        const int t0 = (item / col_groups) * 4, e0 = (item % col_groups) * 128 + lane;
         if (t0 >= count) continue;
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int j = 0; j <= t0 + 3 && j < count; ++j) {
-            const float vv = vs[j * Dv + e];
+        float acc[4][4];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) acc[u] = fmaf(As[(t0 + u) * (L + 1) + j], vv, acc[u]);
+        for (int u = 0; u < 4; ++u) acc[u][0] = acc[u][1] = acc[u][2] = acc[u][3] = 0.f;
+        int e[4];
+#pragma unroll
+        for (int x = 0; x < 4; ++x) e[x] = min(e0 + 32 * x, Dv - 1);      // (columns beyond the last repeat it; not stored)
+        const int j_end = min(t0 + 3, count - 1);
+        for (int j = 0; j <= j_end; ++j) {
+            float a[4], vv[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) a[u] = As[(t0 + u) * (L + 1) + j];
+#pragma unroll
+            for (int x = 0; x < 4; ++x) vv[x] = vs[j * Dv + e[x]];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int x = 0; x < 4; ++x) acc[u][x] = fmaf(a[u], vv[x], acc[u][x]);
         }
         for (int d = 0; d < D; ++d) {
-            const float sv = Ss[d * SP + e];
+            float qv[4], sv[4];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) acc[u] = fmaf(qs[(t0 + u) * (D + 1) + d], sv, acc[u]);
+            for (int u = 0; u < 4; ++u) qv[u] = qs[(t0 + u) * (D + 1) + d];
+#pragma unroll
+            for (int x = 0; x < 4; ++x) sv[x] = Ss[d * SP + e[x]];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int x = 0; x < 4; ++x) acc[u][x] = fmaf(qv[u], sv[x], acc[u][x]);
         }
 #pragma unroll
         for (int u = 0; u < 4; ++u)
-            if (t0 + u < count) p.out[((size_t)(row0 + t0 + u) * p.n_head + h) * Dv + e] = acc[u];
+#pragma unroll
+            for (int x = 0; x < 4; ++x)
+                if (t0 + u < count && e0 + 32 * x < Dv)
+                    p.out[((size_t)(row0 + t0 + u) * p.n_head + h) * Dv + e0 + 32 * x] = acc[u][x];
     }
     if (MLSTM && tid < count) {                                       // the normaliser's column, a row a thread
         const int t = tid;
@@ -301,7 +347,7 @@ __global__ void __launch_bounds__(THREADS) chunk_output_kernel(const ChunkParams
 }
 
 size_t local_smem(int L, int D, int DvE, bool mlstm) {
-    return sizeof(float) * ((size_t)L * (D + 1) + (size_t)L * ((DvE + 7) / 8 * 8) + (mlstm ? 2 * L : 0));
+    return sizeof(float) * ((size_t)L * (D + 1) + (size_t)L * ((DvE + 7) / 8 * 8) + (mlstm ? 2 * L : (size_t)L * (D + 1)));
 }
 size_t output_smem(int L, int D, int Dv, bool mlstm) {
     const int DvE = Dv + (mlstm ? 1 : 0);
