@@ -68,6 +68,7 @@ __device__ __forceinline__ void store4(bf16* p, float a, float b, float c, float
 // L1 cache): the mean, then the biased variance of the centred values, then the affine map.
 // gain and shift (shift may be null) in global or shared memory; src, gain, shift and dst
 // 16-byte aligned (dst 8 for bfloat16).  A row's result depends on nothing but the row.
+// A negative eps asks for the RMS norm instead: no mean is taken off, y = x / sqrt(mean(x^2) + |eps|) * gain.
 template <typename TOut>
 __device__ __forceinline__ void layernorm_row_chunked(const float* src, int width, const float* gain, const float* shift,
                                                       float eps, TOut* dst, int lane) {
@@ -85,7 +86,7 @@ __device__ __forceinline__ void layernorm_row_chunked(const float* src, int widt
 #pragma unroll
         for (int i = 0; i < 8; ++i) sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
     }
-    const float mean = warp_sum(sum) / (float)width;
+    const float mean = eps < 0.f ? 0.f : warp_sum(sum) / (float)width;
     float sq = 0.f;
     for (int i0 = 0; i0 < n4; i0 += 256) {
         float4 v[8];
@@ -100,7 +101,7 @@ __device__ __forceinline__ void layernorm_row_chunked(const float* src, int widt
             sq += (dx * dx + dy * dy) + (dz * dz + dw * dw);
         }
     }
-    const float rstd = 1.0f / sqrtf(warp_sum(sq) / (float)width + eps);
+    const float rstd = 1.0f / sqrtf(warp_sum(sq) / (float)width + fabsf(eps));
     for (int i0 = 0; i0 < n4; i0 += 256) {
         float4 v[8];
 #pragma unroll

@@ -138,7 +138,7 @@ __global__ void __launch_bounds__(THREADS, 1) linear_stream_kernel(const StreamA
                         v[i] = *reinterpret_cast<const float4*>(src + (lane + 32 * i) * 4);
                         sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
                     }
-                const float mean = warp_sum(sum) / (float)K;
+                const float mean = a.eps < 0.f ? 0.f : warp_sum(sum) / (float)K;      // (a negative eps: the RMS norm)
                 float sq = 0.f;
 #pragma unroll
                 for (int i = 0; i < 8; ++i)
@@ -146,7 +146,7 @@ __global__ void __launch_bounds__(THREADS, 1) linear_stream_kernel(const StreamA
                         const float dx = v[i].x - mean, dy = v[i].y - mean, dz = v[i].z - mean, dw = v[i].w - mean;
                         sq += (dx * dx + dy * dy) + (dz * dz + dw * dw);
                     }
-                const float rstd = 1.0f / sqrtf(warp_sum(sq) / (float)K + a.eps);
+                const float rstd = 1.0f / sqrtf(warp_sum(sq) / (float)K + fabsf(a.eps));
                 // gain and shift of four chunks are read before the four results are stored: a store to
                 // shared memory keeps the loads from shared memory behind it in their place
 #pragma unroll

@@ -130,7 +130,7 @@ __device__ __forceinline__ void ln_finish(const float4 (&v)[LN_RESIDENT], int wi
     float sum = 0.f;
 #pragma unroll
     for (int i = 0; i < LN_RESIDENT; ++i) sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
-    const float mean = warp_sum(sum) / (float)width;
+    const float mean = eps < 0.f ? 0.f : warp_sum(sum) / (float)width;      // (a negative eps: the RMS norm)
     // (the same sums in the same order as with a branch per chunk: a chunk past the row adds +0.0)
     float sq = 0.f;
 #pragma unroll
@@ -139,7 +139,7 @@ __device__ __forceinline__ void ln_finish(const float4 (&v)[LN_RESIDENT], int wi
         const float term = (dx * dx + dy * dy) + (dz * dz + dw * dw);
         sq += lane + 32 * i < n4 ? term : 0.f;
     }
-    const float rstd = 1.0f / sqrtf(warp_sum(sq) / (float)width + eps);
+    const float rstd = 1.0f / sqrtf(warp_sum(sq) / (float)width + fabsf(eps));
     // gain and shift of four chunks are read before the four results are stored: a store to shared
     // memory keeps the loads from shared memory behind it in their place (measured: a third faster)
     const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);

@@ -166,7 +166,7 @@ __global__ void __launch_bounds__(THREADS, 1) mlp_fused_kernel(const MlpArgs a) 
 #pragma unroll
             for (int i = 0; i < 8; ++i)
                 if (i < n4) sum += (v[r][i].x + v[r][i].y) + (v[r][i].z + v[r][i].w);
-            const float mean = warp_sum(sum) / (float)C;
+            const float mean = a.eps < 0.f ? 0.f : warp_sum(sum) / (float)C;      // (a negative eps: the RMS norm)
             MG_STAMP(mlp, 9);
             float sq = 0.f;
 #pragma unroll
@@ -175,7 +175,7 @@ __global__ void __launch_bounds__(THREADS, 1) mlp_fused_kernel(const MlpArgs a) 
                     const float dx = v[r][i].x - mean, dy = v[r][i].y - mean, dz = v[r][i].z - mean, dw = v[r][i].w - mean;
                     sq += (dx * dx + dy * dy) + (dz * dz + dw * dw);
                 }
-            const float rstd = 1.0f / sqrtf(warp_sum(sq) / (float)C + a.eps);
+            const float rstd = 1.0f / sqrtf(warp_sum(sq) / (float)C + fabsf(a.eps));
             uint8_t* dst = xs + (size_t)m * xstride;
             // gain and shift of four chunks are read before the four results are stored: a store to
             // shared memory keeps the loads from shared memory behind it in their place

@@ -42,6 +42,19 @@ class DeferredNorm:
         return self.ops.layernorm(x, self.gain, self.shift, self.eps, self.dtype)
 
 
+class DeferredRMSNorm(DeferredNorm):
+    """An RMS norm that has not run yet.  The projection kernels' prologues take it as a LayerNorm without a
+    shift whose eps is negative (they then take no mean off), with ``offset + weight`` as the gain."""
+
+    def __init__(self, ops, x32, weight, gain, eps, offset, out_dtype, rows=None) -> None:
+        super().__init__(ops, x32, gain, None, -abs(float(eps)), out_dtype, rows)
+        self.weight, self.offset = weight, float(offset)
+
+    def materialize(self):
+        x = self.x32 if self.rows is None else self.ops.gather_rows(self.x32, self.rows)
+        return self.ops.rmsnorm(x, self.weight, -self.eps, self.offset, self.dtype)
+
+
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
 
 
@@ -265,6 +278,18 @@ class CudaOps:
         self._run(self.lib.mg_rmsnorm(_ptr(x32), _ptr(weight), _ptr(out), rows, width, float(eps), float(offset),
                                       self._is_bf16(out), self._stream()), "rmsnorm")
         return out
+
+    def defer_rmsnorm(self, x32, weight, eps, offset, out_dtype, rows=None):
+        """An RMS norm to be fused into the projection that consumes it, where that pays."""
+        self._want(x32, torch.float32, "rmsnorm input", 2)
+        gain = weight
+        if offset != 0.0:
+            hit = self._packed.get(("rms gain", weight.data_ptr(), float(offset)))
+            if hit is None or hit[0] is not weight:
+                hit = (weight, (weight + float(offset)).contiguous())     # made once, when a weight is first seen
+                self._packed[("rms gain", weight.data_ptr(), float(offset))] = hit
+            gain = hit[1]
+        return DeferredRMSNorm(self, x32, weight, gain, eps, offset, out_dtype, rows)
 
     def clone(self, x):
         """A copy of a tensor (a device-to-device copy on the current stream)."""

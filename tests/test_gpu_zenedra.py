@@ -621,3 +621,19 @@ def test_command_line_writes_and_generates(tmp_path):
     assert run.returncode == 0, run.stderr[-2000:]
     out = json.loads(run.stdout.strip().splitlines()[-1])
     assert out["token_ids"] == plain_greedy(raw, load_file(folder / "model.safetensors"), prompt, 8)
+
+
+@pytest.mark.parametrize("rows,width,out", [(1, 64, 96), (8, 320, 200), (16, 1024, 512), (5, 1600, 3200), (3, 72, 40), (40, 128, 64)])
+def test_rms_norm_inside_the_projections(ops, rows, width, out):
+    """The RMS norm as the prologue of the small-batch projection kernels (and, where they refuse, as a kernel
+    of its own in front) against norm then product in float64; rows gathered first, as the head does."""
+    gen = torch.Generator().manual_seed(width + rows)
+    x = 2 * torch.randn(rows + 3, width, generator=gen)
+    w, weight = 0.3 * torch.randn(width, generator=gen), torch.randn(out, width, generator=gen) / math.sqrt(width)
+    weight = weight.to(torch.bfloat16)
+    pick = torch.randperm(rows + 3, generator=gen)[:rows].to(torch.int32)
+    want = plain.rms_norm(x[pick.long()].double(), w.double(), 1e-4, 1.0).to(torch.bfloat16).double() @ weight.double().T
+    for rows_arg, xin in ((dev(pick), dev(x)), (None, dev(x[pick.long()]))):
+        y = ops.defer_rmsnorm(xin, dev(w), 1e-4, 1.0, torch.bfloat16, rows_arg)
+        got = ops.linear(y, dev(weight), None, "none", torch.float32)
+        close(got, want, "bfloat16", "rms norm inside a projection", 0.5)
