@@ -27,7 +27,9 @@ MG_GUARD_DECLARE(matrix_memory_chunked)
 
 namespace {
 
-constexpr int THREADS = 256;
+constexpr int THREADS = 512;        // kernels 1 and 3: one CTA of 16 warps per SM hides its own latencies
+constexpr int SCAN_THREADS = 256;   // kernel 2
+constexpr int SCAN_AHEAD = 8;       // chunks whose loads are in flight at once in kernel 2
 
 __device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
 
@@ -158,12 +160,12 @@ __global__ void __launch_bounds__(THREADS) chunk_local_kernel(const ChunkParams 
 
 // ---- kernel 2 ----------------------------------------------------------------------------------------
 template <bool MLSTM>
-__global__ void __launch_bounds__(THREADS) chunk_scan_kernel(const ChunkParams p) {
+__global__ void __launch_bounds__(SCAN_THREADS) chunk_scan_kernel(const ChunkParams p) {
     pdl_trigger();
     pdl_wait();
     const int r = blockIdx.z, h = blockIdx.y;
     const int D = p.d, DvE = p.dv + (MLSTM ? 1 : 0);
-    const int idx = blockIdx.x * THREADS + threadIdx.x;              // element (e, d) of the head's state
+    const int idx = blockIdx.x * SCAN_THREADS + threadIdx.x;              // element (e, d) of the head's state
     const int first = p.req_chunks[2 * r], n = p.req_chunks[2 * r + 1];
     if (n <= 0) return;
     int slot = p.req_state_slot[r];
@@ -178,13 +180,13 @@ __global__ void __launch_bounds__(THREADS) chunk_scan_kernel(const ChunkParams p
     float* m_ptr = slot_base + (size_t)p.n_head * DvE * D + h;
     float S = (mine && !fresh) ? *s_ptr : 0.f;
     float m = (MLSTM && !fresh) ? *m_ptr : 0.f;
-    for (int c0 = first; c0 < first + n; c0 += 4) {
-        float U[4];
+    for (int c0 = first; c0 < first + n; c0 += SCAN_AHEAD) {
+        float U[SCAN_AHEAD];
 #pragma unroll
-        for (int u = 0; u < 4; ++u)                                     // four chunks' loads in flight at once
+        for (int u = 0; u < SCAN_AHEAD; ++u)                            // several chunks' loads in flight at once
             U[u] = (mine && c0 + u < first + n) ? p.chunk_state[((size_t)(c0 + u) * p.n_head + h) * DvE * D + idx] : 0.f;
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < SCAN_AHEAD; ++u) {
             const int c = c0 + u;
             if (c >= first + n) break;
             if (mine) p.chunk_state[((size_t)c * p.n_head + h) * DvE * D + idx] = S;
@@ -366,7 +368,7 @@ int run_chunked(const ChunkParams& p, cudaStream_t s) {
     if (e != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "matrix memory (chunks): %s", cudaGetErrorString(e));
     e = mg_launch(chunk_local_kernel<T, MLSTM>, dim3(p.n_chunks, p.n_head), dim3(THREADS), s1, s, true, p);
     if (e == cudaSuccess)
-        e = mg_launch(chunk_scan_kernel<MLSTM>, dim3(ceil_div(DvE * p.d, THREADS), p.n_head, p.n_requests), dim3(THREADS), 0, s, true, p);
+        e = mg_launch(chunk_scan_kernel<MLSTM>, dim3(ceil_div(DvE * p.d, SCAN_THREADS), p.n_head, p.n_requests), dim3(SCAN_THREADS), 0, s, true, p);
     if (e == cudaSuccess)
         e = mg_launch(chunk_output_kernel<T, MLSTM>, dim3(p.n_chunks, p.n_head), dim3(THREADS), s3, s, true, p);
     if (e != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "matrix memory (chunks): %s", cudaGetErrorString(e));
