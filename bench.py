@@ -573,12 +573,12 @@ def _zenedra_raw(sz: dict, kinds: list, moe: bool, loop: bool, context: int) -> 
     mixers = {
         "attention": {"heads": heads, "kv_heads": sz["kv_heads"], "dim": 64, "vdim": 64, "scale": 0.125,
                       "mask": {"size": 512}},
-        "gla": {"heads": heads // 2, "dim": 64, "vdim": 128, "tau": 16.0},
-        "mlstm": {"heads": heads // 2, "dim": 64, "vdim": 128, "gate_cap": 15.0},
+        "gla": {"heads": heads // 2, "dim": 64, "vdim": 128, "tau": 8.0},
+        "mlstm": {"heads": heads // 2, "dim": 64, "vdim": 128, "gate_cap": 10.0},
     }
     dense = {"kind": "dense", "ff": sz["ff"] * 2 // 3 // 64 * 64}      # three matrices where the others have two
     routed = {"kind": "moe", "expert": {"ff": sz["expert_ff"], "limit": 7.0},
-              "router": {"experts": sz["experts"], "top": sz["top"], "scale": 2.5, "groups": {"count": 4, "keep": 2}},
+              "router": {"experts": sz["experts"], "top": sz["top"], "scale": 2.0, "groups": {"count": 4, "keep": 2}},
               "shared": {"ff": sz["shared_ff"], "limit": 7.0}}
     layers = [{"type": kind, "mixer": dict(mixers[kind]), "mlp": routed if (moe and i % 2) else dense}
               for i, kind in enumerate(kinds)]

@@ -85,8 +85,8 @@ def _config(which: str) -> dict:
     if which == "D":
         layers = [
             {**_attn(4, 2, 64, 4096, 0.125), "mlp": _dense(256)},
-            {**_gla(2, 64, 128, 16.0), "mlp": _dense(256)},
-            {**_mlstm(2, 128, 64, 15.0), "mlp": _moe(8, 2, 64, 2.0, 2.5, (4, 2), (64, 1.0))},
+            {**_gla(2, 64, 128, 12.0), "mlp": _dense(256)},
+            {**_mlstm(2, 128, 64, 20.0), "mlp": _moe(8, 2, 64, 2.5, 1.5, (4, 2), (64, 1.0))},
         ]
         return {"architecture": "Zenedra", "vocab": 384, "width": 128, "max_positions": 640, "layers": layers,
                 "loop": {"start": 1, "stop": 2, "times": 3}, "norm": {"eps": 1e-5},
