@@ -19,8 +19,9 @@ from ..parts.spec import LayerCall, LayerSpec, ModelSpec, PartSpec
 SLOPE_RATE = 8.0        # head h of H takes slope 2^(-8 (h + 1) / H) off a score per position of distance
 
 
-def _norm(cfg: ZenedraConfig, name: str) -> PartSpec:
-    return PartSpec("rmsnorm", {"width": cfg.width, "eps": cfg.norm_eps, "offset": 1.0, "weight_name": name}, "", "norm")
+def _norm(cfg: ZenedraConfig, name: str, optional: bool = False) -> PartSpec:
+    return PartSpec("rmsnorm", {"width": cfg.width, "eps": cfg.norm_eps, "offset": 1.0, "weight_name": name,
+                                "optional": optional}, "", "norm")
 
 
 def _mixer(cfg: ZenedraConfig, m) -> PartSpec:
@@ -53,7 +54,10 @@ def describe_zenedra(cfg: ZenedraConfig) -> ModelSpec:
         p = f"l{i}."
         parts = {"norm1": _norm(cfg, p + "norm1"), "mixer": _mixer(cfg, layer.mixer)}
         arrangement = "pre_norm_mixer_only"
-        if layer.mlp is not None:
+        if layer.mlp is None:
+            # (a checkpoint may still hold the second norm of a layer without a feed-forward)
+            parts["norm2"] = _norm(cfg, p + "norm2", optional=True)
+        else:
             arrangement = "pre_norm"
             parts["norm2"] = _norm(cfg, p + "norm2")
             parts["feed_forward"] = _feed_forward(cfg, layer.mlp)

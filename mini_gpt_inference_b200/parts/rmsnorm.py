@@ -15,15 +15,16 @@ class RMSNorm(Norm):
     graph_safe = True      # launches kernels only; nothing is decided on the host per step
 
     def __init__(self, prefix: str, width: int, eps: float, offset: float = 0.0,
-                 weight_name: str | None = None) -> None:
+                 weight_name: str | None = None, optional: bool = False) -> None:
         super().__init__(prefix)
         self.width, self.eps, self.offset = width, float(eps), float(offset)
+        self.optional = bool(optional)     # a norm that a layer carries but never runs
         self.weight_name = weight_name if weight_name is not None else self.prefix + "weight"
         self.weight = None
 
     def tensor_specs(self):
         init = "norm_shift" if self.offset == 1.0 else "norm_gain"
-        return {self.weight_name: TensorSpec((self.width,), "vector", init)}
+        return {self.weight_name: TensorSpec((self.width,), "vector", init, optional=self.optional)}
 
     def bind(self, tensors) -> None:
         self.weight = tensors.get(self.weight_name)

@@ -392,7 +392,7 @@ def test_gated_gelu_unit_and_pass_entry(ops, dtype):
 
 
 # ---- the step function --------------------------------------------------------------------------
-CASES = [(w, d) for w in "ABCD" for d in ("float32", "bfloat16")]
+CASES = [(w, d) for w in "ABCDEF" for d in ("float32", "bfloat16")]
 IDS = [f"{w}-{d}" for w, d in CASES]
 
 

@@ -91,10 +91,22 @@ def _config(which: str) -> dict:
         return {"architecture": "Zenedra", "vocab": 384, "width": 128, "max_positions": 640, "layers": layers,
                 "loop": {"start": 1, "stop": 2, "times": 3}, "norm": {"eps": 1e-5},
                 "embedding": {"bigram": {"buckets": 256, "mul_prev": 3, "mul_cur": 11}}}
+    if which == "E":                                        # no attention at all: nothing is kept in pages
+        layers = [
+            {**_gla(2, 16, 16, 2.0), "mlp": _dense(64)},
+            {**_mlstm(2, 16, 24, 5.0), "mlp": None},
+        ]
+        return {"architecture": "Zenedra", "vocab": 64, "width": 40, "max_positions": 200, "layers": layers,
+                "norm": {"eps": 1e-5}, "embedding": {"bigram": {"buckets": 13, "mul_prev": 2, "mul_cur": 3}}}
+    if which == "F":                                        # attention alone, three passes over the one layer
+        layers = [{**_attn(2, 1, 32, 10, 0.2), "mlp": _dense(48)}]
+        return {"architecture": "Zenedra", "vocab": 80, "width": 48, "max_positions": 200, "layers": layers,
+                "loop": {"start": 0, "stop": 1, "times": 3}, "norm": {"eps": 1e-5},
+                "embedding": {"bigram": {"buckets": 31, "mul_prev": 7, "mul_cur": 1}}}
     raise KeyError(which)
 
 
-PAGE_TOKENS = {"A": 8, "B": 16, "C": 4, "D": 16}
+PAGE_TOKENS = {"A": 8, "B": 16, "C": 4, "D": 16, "E": 8, "F": 4}
 DECAY_RANK = {"A": 4, "B": 7, "C": 16, "D": 8}
 
 
