@@ -550,6 +550,25 @@ def test_greedy_generation_through_the_engine(which, dtype):
     engine.runner.manager.check()
 
 
+def test_preemption_and_recompute_through_the_engine():
+    """A pool too small for the three running requests (the attention's block made longer than any sequence, so
+    that no page comes back early): requests are preempted, give back their pages and state slot, and are
+    computed again from their first token in a slot that another request used meanwhile."""
+    raw = config("A")
+    raw["layers"][1]["mixer"]["mask"]["size"] = 1000
+    tensors = random_weights(raw, 14)
+    loaded = load_model(config=ZenedraConfig.from_dict(raw), tensors=tensors, dtype="float32", device="cuda:0")
+    engine = LLMEngine(loaded, EngineConfig(dtype="float32", block_size=8, num_blocks=10, max_batch_size=3,
+                                            max_num_batched_tokens=16, max_prefill_chunk=7))
+    prompts = [tokens_for(raw, n, 60 + i) for i, n in enumerate([20, 25, 18, 9])]
+    outs = engine.generate(prompts, SamplingParams(max_tokens=16, temperature=0.0))
+    assert engine.scheduler.num_preemptions > 0
+    for prompt, out in zip(prompts, outs):
+        assert out["token_ids"] == plain_greedy(raw, tensors, prompt, 16)
+    assert engine.stats()["allocated_blocks"] == 0
+    engine.runner.manager.check()
+
+
 def test_long_decoding_through_the_engine():
     raw = config("B")
     tensors = random_weights(raw, 12)
