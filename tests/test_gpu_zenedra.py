@@ -172,8 +172,8 @@ def test_matrix_memory_prompt_portions_and_single_tokens(ops, dtype, mode, heads
 @pytest.mark.parametrize("heads,d,dv", [(2, 24, 40), (1, 8, 33), (2, 64, 128), (1, 128, 200), (1, 200, 16)])
 def test_matrix_memory_chunk_by_chunk(ops, dtype, mode, strong, heads, d, dv):
     """The chunked form that serves prompt portions, against the plain mixer: three requests of unequal
-    lengths in one step (chunks that are full, partial and of one token), then a second step that goes on
-    from the state slots the first one left; the work list is made by the kernel set's own planner.  The
+    lengths in one step (chunks that are full, partial and of one token), then two more steps that go on
+    from the state slots the one before left; the work list is made by the kernel set's own planner.  The
     kernels take 32-bit rows too (the engine gives them bfloat16 steps only), which is the sharp comparison.
     ``strong``: decays and gates so strong that a chunk's first token is forgotten many times over by its
     end, which must not overflow anything."""
@@ -191,13 +191,14 @@ def test_matrix_memory_chunk_by_chunk(ops, dtype, mode, strong, heads, d, dv):
     if dtype == "bfloat16":
         w = {k: v.to(torch.bfloat16).float() for k, v in w.items()}
     wd = {k: v.double() for k, v in w.items()}
-    h = [torch.randn(n, c, generator=gen) for n in (150, 70, 33)]
+    h = [torch.randn(n, c, generator=gen) for n in (150, 70, 60)]
     mixer = plain.gla_mixer if mode == "gla" else plain.mlstm_mixer
     want = [mixer(x.double(), wd, "", m, eps) for x in h]
     cols = dv + (1 if mode == "mlstm" else 0)
     state = torch.full((5, heads * cols * d + heads), float("nan"), device="cuda:0")
     got = [[], [], []]
-    for portions, before in (([100, 70, 5], [0, 0, 0]), ([50, 0, 28], [100, 70, 5])):
+    # (the second and third step: a single token beside a long portion, each way round)
+    for portions, before in (([100, 70, 5], [0, 0, 0]), ([49, 0, 1], [100, 70, 5]), ([1, 0, 54], [149, 70, 6])):
         live = [r for r in range(3) if portions[r]]
         x = torch.cat([h[r][before[r]: before[r] + portions[r]] for r in live]).double()
         proj = dev(torch.cat([x @ wd[k].T for k in ("q", "k", "v", "g")], dim=1), t)
