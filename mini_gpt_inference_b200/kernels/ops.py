@@ -326,8 +326,8 @@ class CudaOps:
         n, width = ctx.token_ids.numel(), tok_emb.shape[1]
         if pair_emb.shape != (buckets + 1, width) or (pos_table is not None and pos_table.shape[1] != width):
             raise KernelLibraryError("embed_pairs: the tables do not fit")
-        if (buckets - 1) * (int(mul_prev) + int(mul_cur)) >= 2 ** 62 or tok_emb.shape[0] * (int(mul_prev) + int(mul_cur)) >= 2 ** 62:
-            raise KernelLibraryError("embed_pairs: the multipliers overflow 64 bits")
+        if not (0 <= int(mul_prev) < 2 ** 31 and 0 <= int(mul_cur) < 2 ** 31 and 0 < int(buckets) < 2 ** 31):
+            raise KernelLibraryError("embed_pairs: buckets and multipliers must fit 31 bits")
         out = torch.empty((n, width), dtype=torch.float32, device=self.device)
         self._run(self.lib.mg_embed_pairs(
             _ptr(ctx.token_ids), _ptr(ctx.positions), _ptr(ctx.token_request), _ptr(ctx.req_q_start), _ptr(ctx.req_q_len),
